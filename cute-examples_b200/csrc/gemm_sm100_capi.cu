@@ -1,0 +1,387 @@
+// Host launcher and C ABI (include/gemm_sm100.h) of the sm_100a TN GEMM.
+// Compiled by nvcc alone: no torch headers in this translation unit (the reference's
+// launcher sm90a/gemm_test.cu:9-10 pulls torch/extension.h into its .cu file).
+//
+// What the reference does per call in test::gemm_tn_test (gemm_test.cu:12-92) and where
+// it is here:  argument checks :15-41 -> validate();  CuTe tensor-map construction
+// :56-68 -> encode_2d() through the driver entry point;  grid = min(132, tiles) :70-72 ->
+// persistent grid from the device's SM count and cluster occupancy;  cluster launch
+// :82-85 -> cudaLaunchKernelEx on the caller's stream;  sync + exit on error :86 ->
+// asynchronous, errors returned.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/gemm_sm100.h"
+#include "gemm_tn_sm100.cuh"
+
+namespace {
+
+using namespace gemm_sm100;
+
+// One status word per device (a __device__ variable exists once per device).
+__device__ unsigned int g_status_word;
+
+constexpr int kMaxDevices = 64;
+constexpr int kNumConfigs = 4;
+
+struct ConfigInfo {
+  int cta_group, block_n, stages;
+};
+constexpr ConfigInfo kConfigs[kNumConfigs] = {
+    {2, 256, 6},
+    {2, 128, 8},
+    {1, 256, 4},
+    {1, 128, 6},
+};
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  unsigned int* status_ptr = nullptr;
+  int max_ctas[kNumConfigs][2] = {};   // persistent grid limit per config and dtype
+  bool attr_set[kNumConfigs][2] = {};
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+long g_opt_tile_config = -1;
+long g_opt_timeout_ms = 2000;
+long g_opt_max_ctas = 0;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int set_cuda_error(int* out, cudaError_t e) {
+  if (out) *out = static_cast<int>(e);
+  return GEMM_SM100_ERR_CUDA;
+}
+
+// Looks the driver's tensor-map encoder up once (no link-time dependency on libcuda).
+int get_encoder(int* cuda_error_out) {
+  if (g_encode) return GEMM_SM100_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+    return set_cuda_error(cuda_error_out, cudaErrorSymbolNotFound);
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return GEMM_SM100_OK;
+}
+
+// Tensor map of a row-major 2-D array of 16-bit elements: `rows` x `cols`, pitch `ld`
+// elements, box `box_rows` x 64 columns, 128-byte swizzle (64 x 2 B = one swizzle row).
+int encode_2d(CUtensorMap* map, const void* base, int dtype, long rows, long cols, long ld,
+              int box_rows, int* cuda_error_out) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUtensorMapDataType dt =
+      dtype == GEMM_SM100_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_cuda_error(cuda_error_out, cudaErrorInvalidValue);
+  return GEMM_SM100_OK;
+}
+
+int device_state(DeviceState** out, int* cuda_error_out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  if (dev < 0 || dev >= kMaxDevices) return set_cuda_error(cuda_error_out, cudaErrorInvalidDevice);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    e = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    e = cudaDeviceGetAttribute(&st.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    if (st.cc_major != 10) return GEMM_SM100_ERR_UNSUPPORTED_DEVICE;
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_status_word);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    st.status_ptr = static_cast<unsigned int*>(p);
+    e = cudaMemset(st.status_ptr, 0, sizeof(unsigned int));
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    st.ready = true;
+  }
+  *out = &st;
+  return GEMM_SM100_OK;
+}
+
+struct Problem {
+  const void* A;
+  const void* B;
+  void* C;
+  int M, N, K;
+  long lda, ldb, ldc;
+  int dtype;
+};
+
+int validate(const Problem& p) {
+  if (p.M < 0 || p.N < 0 || p.K < 0) return GEMM_SM100_ERR_BAD_SHAPE;
+  if (p.dtype != GEMM_SM100_BF16 && p.dtype != GEMM_SM100_FP16) return GEMM_SM100_ERR_UNSUPPORTED_DTYPE;
+  if (p.M == 0 || p.N == 0) return GEMM_SM100_OK;
+  if (!p.C || (p.K > 0 && (!p.A || !p.B))) return GEMM_SM100_ERR_NULL_POINTER;
+  if (p.K % 8 != 0) return GEMM_SM100_ERR_BAD_SHAPE;
+  if (p.lda < p.K || p.ldb < p.K || p.ldc < p.N) return GEMM_SM100_ERR_BAD_SHAPE;
+  if (p.lda % 8 != 0 || p.ldb % 8 != 0 || p.ldc % 8 != 0) return GEMM_SM100_ERR_BAD_ALIGNMENT;
+  if ((reinterpret_cast<uintptr_t>(p.A) | reinterpret_cast<uintptr_t>(p.B) |
+       reinterpret_cast<uintptr_t>(p.C)) & 15u)
+    return GEMM_SM100_ERR_BAD_ALIGNMENT;
+  return GEMM_SM100_OK;
+}
+
+inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
+
+// Cost model used to choose a tile configuration: time ~ waves x (work of one tile),
+// where a wave is one tile on every resident CTA pair.  Narrow tiles pay a little more
+// shared-memory traffic per flop, single-CTA tiles twice the B traffic.
+int choose_config(const Problem& p, int sm_count) {
+  if (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) return static_cast<int>(g_opt_tile_config);
+  double best = 1e300;
+  int best_i = 0;
+  for (int i = 0; i < kNumConfigs; ++i) {
+    const ConfigInfo& c = kConfigs[i];
+    const long tiles = ceil_div(p.M, 128L * c.cta_group) * ceil_div(p.N, c.block_n);
+    const long slots = sm_count / c.cta_group;
+    const long waves = ceil_div(tiles, slots);
+    double tile_cost = static_cast<double>(c.block_n) / 256.0;   // per-CTA MMA time of one tile
+    if (c.block_n == 128) tile_cost *= 1.06;
+    if (c.cta_group == 1) tile_cost *= 1.15;
+    const double cost = static_cast<double>(waves) * tile_cost;
+    if (cost < best) {
+      best = cost;
+      best_i = i;
+    }
+  }
+  return best_i;
+}
+
+template <int kCfgIndex, bool kIsBf16>
+int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
+  constexpr ConfigInfo ci = kConfigs[kCfgIndex];
+  using Cfg = GemmConfig<ci.cta_group, ci.block_n, ci.stages, kIsBf16>;
+  auto kernel = gemm_tn_kernel<Cfg>;
+  constexpr int dt = kIsBf16 ? 0 : 1;
+  cudaError_t e;
+
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!st.attr_set[kCfgIndex][dt]) {
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      int max_ctas = st.sm_count;
+      if (Cfg::kCtaGroup == 2) {
+        cudaLaunchConfig_t qc = {};
+        qc.gridDim = dim3(st.sm_count - st.sm_count % 2);
+        qc.blockDim = dim3(Cfg::kThreads);
+        qc.dynamicSmemBytes = Cfg::kSmemBytes;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        qc.attrs = qa;
+        qc.numAttrs = 1;
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &qc);
+        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+        if (clusters < 1) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
+        max_ctas = 2 * clusters;
+        if (max_ctas > st.sm_count) max_ctas = st.sm_count - st.sm_count % 2;
+      }
+      st.max_ctas[kCfgIndex][dt] = max_ctas;
+      st.attr_set[kCfgIndex][dt] = true;
+    }
+  }
+
+  TileParams tp;
+  tp.M = p.M;
+  tp.N = p.N;
+  tp.K = p.K;
+  tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
+  tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
+  tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
+  tp.group_m = Cfg::kCtaGroup == 2 ? 8 : 16;
+  tp.status = st.status_ptr;
+  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
+
+  CUtensorMap map_a, map_b, map_c;
+  int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  if (rc) return rc;
+  rc = encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
+  if (rc) return rc;
+  rc = encode_2d(&map_c, p.C, p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
+  if (rc) return rc;
+
+  long ctas = static_cast<long>(tp.m_tiles) * tp.n_tiles * Cfg::kCtaGroup;
+  long cap = st.max_ctas[kCfgIndex][dt];
+  if (g_opt_max_ctas > 0 && g_opt_max_ctas < cap) cap = g_opt_max_ctas - g_opt_max_ctas % Cfg::kCtaGroup;
+  if (cap < Cfg::kCtaGroup) cap = Cfg::kCtaGroup;
+  if (ctas > cap) ctas = cap;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = Cfg::kCtaGroup;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  return GEMM_SM100_OK;
+}
+
+template <bool kIsBf16>
+int dispatch(int config, const Problem& p, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
+  switch (config) {
+    case 0: return launch_config<0, kIsBf16>(p, st, stream, cuda_error_out);
+    case 1: return launch_config<1, kIsBf16>(p, st, stream, cuda_error_out);
+    case 2: return launch_config<2, kIsBf16>(p, st, stream, cuda_error_out);
+    case 3: return launch_config<3, kIsBf16>(p, st, stream, cuda_error_out);
+    default: return GEMM_SM100_ERR_BAD_OPTION;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
+                  long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
+                  int* cuda_error_out) {
+  (void)workspace;
+  (void)workspace_bytes;
+  if (cuda_error_out) *cuda_error_out = 0;
+  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype};
+  int rc = validate(p);
+  if (rc != GEMM_SM100_OK) return rc;
+  if (M == 0 || N == 0) return GEMM_SM100_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (K == 0) {
+    cudaError_t e = cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 2, 0, static_cast<size_t>(N) * 2,
+                                      static_cast<size_t>(M), stream);
+    return e == cudaSuccess ? GEMM_SM100_OK : set_cuda_error(cuda_error_out, e);
+  }
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    rc = get_encoder(cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+  }
+  const int config = choose_config(p, st->sm_count);
+  if (dtype == GEMM_SM100_BF16) return dispatch<true>(config, p, *st, stream, cuda_error_out);
+  return dispatch<false>(config, p, *st, stream, cuda_error_out);
+}
+
+size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype) {
+  (void)M;
+  (void)N;
+  (void)K;
+  (void)dtype;
+  return 0;
+}
+
+int gemm_sm100_num_sms(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  return n;
+}
+
+int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  if (status_out) *status_out = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+  }
+  unsigned int word = 0;
+  e = cudaMemcpy(&word, st->status_ptr, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  if (status_out) *status_out = word;
+  if (word != 0) {
+    e = cudaMemset(st->status_ptr, 0, sizeof(word));
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    return GEMM_SM100_ERR_DEVICE_TIMEOUT;
+  }
+  return GEMM_SM100_OK;
+}
+
+int gemm_sm100_set_option(const char* name, long value) {
+  if (!name) return GEMM_SM100_ERR_NULL_POINTER;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (std::strcmp(name, "tile_config") == 0) {
+    if (value < -1 || value >= kNumConfigs) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_tile_config = value;
+    return GEMM_SM100_OK;
+  }
+  if (std::strcmp(name, "timeout_ms") == 0) {
+    if (value < 1 || value > 60000) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_timeout_ms = value;
+    return GEMM_SM100_OK;
+  }
+  if (std::strcmp(name, "max_ctas") == 0) {
+    if (value < 0) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_max_ctas = value;
+    return GEMM_SM100_OK;
+  }
+  return GEMM_SM100_ERR_BAD_OPTION;
+}
+
+int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes) {
+  if (!buf || buf_bytes == 0) return GEMM_SM100_ERR_NULL_POINTER;
+  if (index < 0 || index >= kNumConfigs) return GEMM_SM100_ERR_BAD_OPTION;
+  const ConfigInfo& c = kConfigs[index];
+  std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d", c.cta_group,
+                128 * c.cta_group, c.block_n, c.stages, 2 * c.block_n);
+  return GEMM_SM100_OK;
+}
+
+int gemm_sm100_select_config(int M, int N, int K, int dtype) {
+  Problem p{nullptr, nullptr, nullptr, M, N, K, K, K, N, dtype};
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  int sms = gemm_sm100_num_sms();
+  if (sms <= 0) sms = 148;
+  return choose_config(p, sms);
+}
+
+const char* gemm_sm100_error_string(int code) {
+  switch (code) {
+    case GEMM_SM100_OK: return "ok";
+    case GEMM_SM100_ERR_NULL_POINTER: return "null pointer";
+    case GEMM_SM100_ERR_BAD_SHAPE: return "bad shape (negative extent, K not a multiple of 8, or leading dimension too small)";
+    case GEMM_SM100_ERR_BAD_ALIGNMENT: return "pointer or row pitch not 16-byte aligned";
+    case GEMM_SM100_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype (bf16 = 0, fp16 = 1)";
+    case GEMM_SM100_ERR_CUDA: return "CUDA error";
+    case GEMM_SM100_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case GEMM_SM100_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case GEMM_SM100_ERR_UNSUPPORTED_DEVICE: return "device is not sm_100";
+    case GEMM_SM100_ERR_BAD_OPTION: return "unknown option or value out of range";
+    default: return "unknown error code";
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,121 @@
+// PyTorch binding of the sm_100a TN GEMM: module gemm_kernels._C.
+// Same module name, function name, argument names and order as the reference's binding
+// (kernels/gemm_kernels/__init__.cpp:6-9): gemm_tn_test(A, B, C) writes A * B^T into the
+// caller's C and returns that same tensor (kernels/gemm_kernels/sm90a/gemm_test.cu:91).
+// All device work happens behind the C ABI of include/gemm_sm100.h; this file only checks
+// tensors and hands over pointers, sizes and the current stream.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <string>
+
+#include "../../include/gemm_sm100.h"
+
+namespace test {
+
+namespace {
+
+void raise_for(int rc, int cuda_error, const char* what) {
+  if (rc == GEMM_SM100_OK) return;
+  std::string msg = std::string(what) + ": " + gemm_sm100_error_string(rc);
+  if (rc == GEMM_SM100_ERR_CUDA) msg += " (cudaError_t " + std::to_string(cuda_error) + ")";
+  TORCH_CHECK(false, msg);
+}
+
+int dtype_code(const torch::Tensor& t) {
+  if (t.scalar_type() == torch::kBFloat16) return GEMM_SM100_BF16;
+  if (t.scalar_type() == torch::kFloat16) return GEMM_SM100_FP16;
+  TORCH_CHECK(false, "Both tensors must be of type bfloat16 or float16");
+  return -1;
+}
+
+}  // namespace
+
+// Checks follow the reference's order and wording where it has them (gemm_test.cu:15-41);
+// C is checked as well (the reference assumes it), tile-divisibility is not required.
+torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::Tensor C) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "All tensors must be CUDA tensors");
+  TORCH_CHECK(A.device() == B.device() && A.device() == C.device(),
+              "All tensors must be on the same device");
+  TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "All tensors must be contiguous");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "Both tensors must be 2D (matrix) tensors");
+  TORCH_CHECK(A.size(1) == B.size(1), "Inner dimensions of A and B must match (A: ", A.size(1),
+              ", B: ", B.size(1), ")");
+  const int dtype = dtype_code(A);
+  TORCH_CHECK(B.scalar_type() == A.scalar_type() && C.scalar_type() == A.scalar_type(),
+              "A, B and C must have the same dtype");
+  TORCH_CHECK(C.dim() == 2 && C.size(0) == A.size(0) && C.size(1) == B.size(0),
+              "C must be a 2D tensor of shape [A.size(0), B.size(0)]");
+  TORCH_CHECK(C.numel() == 0 || C.stride(1) == 1, "C must have unit stride along its last dimension");
+  TORCH_CHECK(A.size(0) <= INT32_MAX && B.size(0) <= INT32_MAX && A.size(1) <= INT32_MAX,
+              "extents must fit in 32 bits");
+  const int M = static_cast<int>(A.size(0));
+  const int N = static_cast<int>(B.size(0));
+  const int K = static_cast<int>(A.size(1));
+  if (M == 0 || N == 0) return C;
+
+  c10::cuda::CUDAGuard guard(A.device());
+  const size_t ws_bytes = gemm_sm100_workspace_bytes(M, N, K, dtype);
+  torch::Tensor workspace;
+  void* ws_ptr = nullptr;
+  if (ws_bytes > 0) {
+    workspace = torch::empty({static_cast<int64_t>(ws_bytes)},
+                             torch::TensorOptions().dtype(torch::kUInt8).device(A.device()));
+    ws_ptr = workspace.data_ptr();
+  }
+  cudaStream_t stream = c10::cuda::getCurrentCUDAStream(A.device().index()).stream();
+  const long ldc = M > 1 ? static_cast<long>(C.stride(0)) : static_cast<long>(N);
+  int cuda_error = 0;
+  int rc;
+  {
+    pybind11::gil_scoped_release release;
+    rc = gemm_sm100_tn(A.const_data_ptr(), B.const_data_ptr(), C.mutable_data_ptr(), M, N, K,
+                       static_cast<long>(K), static_cast<long>(K), ldc, dtype, ws_ptr, ws_bytes,
+                       static_cast<void*>(stream), &cuda_error);
+  }
+  raise_for(rc, cuda_error, "gemm_tn_test");
+  return C;
+}
+
+// Waits for the current device and raises if a kernel reported a timed-out wait.
+unsigned int device_status() {
+  unsigned int word = 0;
+  int cuda_error = 0;
+  int rc;
+  {
+    pybind11::gil_scoped_release release;
+    rc = gemm_sm100_device_status(&word, &cuda_error);
+  }
+  if (rc == GEMM_SM100_ERR_DEVICE_TIMEOUT) {
+    TORCH_CHECK(false, "gemm_sm100: device-side wait timed out, status word 0x", std::hex, word);
+  }
+  raise_for(rc, cuda_error, "device_status");
+  return word;
+}
+
+void set_option(const std::string& name, long value) {
+  raise_for(gemm_sm100_set_option(name.c_str(), value), 0, "set_option");
+}
+
+std::string describe_config(int index) {
+  char buf[256];
+  raise_for(gemm_sm100_describe_config(index, buf, sizeof(buf)), 0, "describe_config");
+  return std::string(buf);
+}
+
+PYBIND11_MODULE(_C, m) {
+  m.def("gemm_tn_test", &gemm_tn_test, "GEMM transpose-normal test function", pybind11::arg("A"),
+        pybind11::arg("B"), pybind11::arg("C"));
+  m.def("device_status", &device_status,
+        "Synchronise the current device and raise if a GEMM kernel reported a failed wait");
+  m.def("set_option", &set_option, pybind11::arg("name"), pybind11::arg("value"));
+  m.def("describe_config", &describe_config, pybind11::arg("index"));
+  m.def("select_config", &gemm_sm100_select_config, pybind11::arg("M"), pybind11::arg("N"),
+        pybind11::arg("K"), pybind11::arg("dtype"));
+  m.def("workspace_bytes", &gemm_sm100_workspace_bytes, pybind11::arg("M"), pybind11::arg("N"),
+        pybind11::arg("K"), pybind11::arg("dtype"));
+  m.def("num_sms", &gemm_sm100_num_sms);
+}
+
+}  // namespace test

@@ -1,0 +1,55 @@
+"""gemm_kernels: B200 (sm_100a) TN GEMM behind the reference's Python entry point.
+
+``gemm_tn_test(A, B, C)`` computes ``C[M,N] = A[M,K] @ B[N,K].T`` (bf16 or fp16 inputs,
+fp32 accumulation, same-dtype output), writes it into the caller's ``C`` and returns ``C``:
+the contract of the reference's ``gemm_kernels._C.gemm_tn_test``
+(kernels/gemm_kernels/__init__.cpp:6-9, kernels/gemm_kernels/sm90a/gemm_test.cu:12-92).
+
+The reference's package ``__init__.py`` is empty, so its own scripts'
+``from gemm_kernels import gemm_tn_test`` (kernels/tests/gemm_test.py:2) cannot resolve;
+this module re-exports the symbol so that import works, and keeps ``gemm_kernels._C``.
+
+There is no CPU or eager fallback: importing this package without the compiled extension
+raises ImportError with the build command.
+"""
+from __future__ import annotations
+
+import os as _os
+
+try:
+    from . import _C  # noqa: F401
+except ImportError as exc:  # pragma: no cover - exercised only on an unbuilt tree
+    _here = _os.path.dirname(_os.path.abspath(__file__))
+    raise ImportError(
+        "gemm_kernels._C is not built (sm_100a only, no fallback path). Build it in-tree with "
+        f"`python {_os.path.join(_os.path.dirname(_here), 'build_native.py')}`"
+    ) from exc
+
+import torch as _torch
+
+gemm_tn_test = _C.gemm_tn_test
+device_status = _C.device_status
+set_option = _C.set_option
+describe_config = _C.describe_config
+select_config = _C.select_config
+workspace_bytes = _C.workspace_bytes
+num_sms = _C.num_sms
+
+LIBRARY_PATH = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "libgemm_sm100.so")
+
+DTYPE_CODES = {_torch.bfloat16: 0, _torch.float16: 1}
+
+
+def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" = None) -> "_torch.Tensor":
+    """``A[M,K] @ B[N,K].T`` into ``out`` (allocated as ``[M,N]`` of A's dtype when None)."""
+    if out is None:
+        out = _torch.empty((A.shape[0], B.shape[0]), dtype=A.dtype, device=A.device)
+    return gemm_tn_test(A, B, out)
+
+
+from .nsplit import NSplitPlan, gemm_tn_nsplit, shard_rows  # noqa: E402
+
+__all__ = [
+    "gemm_tn_test", "gemm_tn", "gemm_tn_nsplit", "NSplitPlan", "shard_rows", "device_status",
+    "set_option", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
+]

@@ -1,0 +1,93 @@
+/* C ABI of the B200 (sm_100a) TN GEMM:  C[M,N] = A[M,K] * B[N,K]^T,
+ * 16-bit inputs (bf16 or fp16), fp32 accumulation, same-dtype output (round to nearest even).
+ *
+ * This is the native boundary underneath the Python entry point
+ * gemm_kernels._C.gemm_tn_test(A, B, C).  The reference has no C ABI: its native entry
+ * is the C++ function test::gemm_tn_test(torch::Tensor, torch::Tensor, torch::Tensor)
+ * (kernels/gemm_kernels/sm90a/gemm_test.cu:12-92), bound by pybind11 in
+ * kernels/gemm_kernels/__init__.cpp:6-9.  The functions below carry that function's
+ * contract with plain pointers and sizes; the library is compiled without torch.
+ *
+ * All pointers are device pointers on the CURRENT CUDA device unless stated otherwise.
+ * Nothing here allocates device memory and nothing calls exit(): every failure is a
+ * return code (the reference prints and exits on a CUDA error, gemm_test.cu:78,86).
+ */
+#ifndef GEMM_SM100_H_
+#define GEMM_SM100_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes. */
+#define GEMM_SM100_OK 0
+#define GEMM_SM100_ERR_NULL_POINTER 1
+#define GEMM_SM100_ERR_BAD_SHAPE 2        /* negative extent, K not a multiple of 8, ld too small */
+#define GEMM_SM100_ERR_BAD_ALIGNMENT 3    /* base pointer or row pitch not 16-byte aligned */
+#define GEMM_SM100_ERR_UNSUPPORTED_DTYPE 4
+#define GEMM_SM100_ERR_CUDA 5             /* a CUDA call failed; *cuda_error_out holds the cudaError_t */
+#define GEMM_SM100_ERR_DEVICE_TIMEOUT 6   /* a bounded device-side wait ran out (see gemm_sm100_device_status) */
+#define GEMM_SM100_ERR_WORKSPACE 7        /* workspace missing, misaligned or too small */
+#define GEMM_SM100_ERR_UNSUPPORTED_DEVICE 8 /* current device is not compute capability 10.x */
+#define GEMM_SM100_ERR_BAD_OPTION 9
+
+/* Element types of A, B and C. */
+#define GEMM_SM100_BF16 0
+#define GEMM_SM100_FP16 1
+
+/* Enqueues C = A * B^T on `cuda_stream` (a cudaStream_t; NULL = legacy default stream)
+ * and returns without waiting for the GPU.
+ *   A: M rows of K elements, row pitch lda (elements);  B: N rows of K elements, pitch ldb;
+ *   C: M rows of N elements, pitch ldc.  "TN": both operands have K contiguous.
+ * Requirements: K % 8 == 0, lda/ldb/ldc % 8 == 0, all three base pointers 16-byte aligned,
+ * lda, ldb >= K, ldc >= N.  M and N are arbitrary (the reference requires M % 256 == 0,
+ * N % 256 == 0, K % 64 == 0: gemm_test.cu:32-41).  M == 0 or N == 0 is a no-op; K == 0 zero-fills C.
+ * `workspace` must hold gemm_sm100_workspace_bytes(M, N, K, dtype) bytes (256-byte aligned)
+ * when that is non-zero; it may be NULL otherwise.
+ * Replaces: test::gemm_tn_test, gemm_test.cu:12-92 (argument checks :15-41, tensor-map
+ * construction :56-68, launch :70-85).  Differences by design: asynchronous on the caller's
+ * stream (the reference uses the legacy default stream and then cudaDeviceSynchronize, :82-86).
+ */
+int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
+                  long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
+                  int* cuda_error_out);
+
+/* Bytes of scratch memory gemm_sm100_tn needs for this problem (0 for most shapes; non-zero
+ * when the memory-bound small-M path splits K).  No reference counterpart: the reference
+ * kernel needs no workspace (gemm_test.cu:70-85). */
+size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype);
+
+/* Number of SMs of the current device (the persistent grid is sized from it; the
+ * reference hard-codes 132, gemm_test.cu:72).  Returns a negative value on error. */
+int gemm_sm100_num_sms(void);
+
+/* Waits for the current device to finish, then reads and clears the device status word
+ * that the kernels set when a bounded wait runs out.  *status_out receives the raw word
+ * (0 = no failure).  Returns GEMM_SM100_OK, GEMM_SM100_ERR_DEVICE_TIMEOUT or
+ * GEMM_SM100_ERR_CUDA.  Replaces the reference's CUTE_CHECK_LAST() after the launch
+ * (gemm_test.cu:86), which synchronises and exits the process on error. */
+int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
+
+/* Tuning / test knobs, process-wide.  Names: "tile_config" (-1 = choose automatically,
+ * otherwise an index reported by gemm_sm100_describe_config), "timeout_ms" (bound of each
+ * device-side wait, default 2000), "max_ctas" (0 = all SMs; caps the persistent grid).
+ * The reference's equivalents are compile-time constants (gemm.cuh:420-451). */
+int gemm_sm100_set_option(const char* name, long value);
+
+/* Writes a short description of tile configuration `index` ("cta_group=2 tile=256x256x64
+ * stages=6 ...") into buf; returns GEMM_SM100_ERR_BAD_OPTION past the last index. */
+int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes);
+
+/* Index of the tile configuration gemm_sm100_tn would pick for this problem on the current
+ * device (negative on error). */
+int gemm_sm100_select_config(int M, int N, int K, int dtype);
+
+/* Static, human-readable name of a return code. */
+const char* gemm_sm100_error_string(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEMM_SM100_H_ */
