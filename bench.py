@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the sm_100a TN GEMM behind gemm_kernels.gemm_tn_test.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one synthetic
+batch:
+  * N = 1: the square bf16 GEMM M=N=K=8192 (BASELINE config 2; operands ~N(0,1)/sqrt(K), seed 1).
+  * N > 1: the large GEMM M=N=K=32768 (BASELINE config 5, seed 4) with B sharded by rows over the
+    ranks, every rank computing its column slab of C and the slabs assembled on every rank by
+    an NCCL all-gather: strong scaling, `value` = 2*M*N*K / (max over ranks of the step time).
+`value` is timed with CUDA events on the launching stream, operands resident in HBM.
+`e2e` is the same step through the public Python entry point with pinned HOST operands and a
+HOST result: host->device copies of A and B and the device->host copy of C are inside the
+timed region.  `roofline` compares the GEMM kernel with the measured cuBLAS bf16 peak of this
+pool (MEASURED_PEAKS.json, else the stated fallback).  `cpu_baseline` times the CPU oracle
+(the reference's check expression, torch fp32 matmul) on the host cores.
+
+--impl reference: the reference's implementation of this path is sm_90a device code that cannot
+run on sm_100 and has no CPU code; its own ground truth, torch.matmul(A.float(), B.float().T)
+(kernels/tests/gemm_test.py:36), timed on the host cores on a bounded slab of the same workload,
+stands in (cpu_baseline.kind = "port").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+sys.path.insert(0, str(REPO / "cute-examples_b200"))
+
+import torch  # noqa: E402
+
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def load_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            if d.get("bf16_tflops") and d.get("hbm_gbs"):
+                return d, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def gemm_flops(M, N, K):
+    return 2.0 * M * N * K
+
+
+def gemm_bytes(M, N, K, esize=2):
+    """Algorithmic bytes: each operand read once, C written once."""
+    return float(esize) * (M * K + N * K + M * N)
+
+
+# ------------------------------------------------------------------ clocks ---
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while the timed
+    region runs."""
+
+    REASONS = {
+        0x0000000000000004: "sw_power_cap",
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+        0x0000000000000080: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "power_w_max": round(max(self.power), 1) if self.power else None}
+
+
+# ------------------------------------------------------------- GPU helpers ---
+def device_inputs(M, N, K, seed, dtype, device, a_std=None, b_std=None):
+    """Seeded operands of the BASELINE distributions, drawn on the device (statistically the
+    same as the CPU generator the parity tests use; bench inputs are not compared bitwise)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    sa = (1.0 / K ** 0.5) if a_std is None else a_std
+    sb = (1.0 / K ** 0.5) if b_std is None else b_std
+    A = (torch.randn((M, K), generator=g, device=device, dtype=torch.float32) * sa).to(dtype)
+    B = (torch.randn((N, K), generator=g, device=device, dtype=torch.float32) * sb).to(dtype)
+    return A, B
+
+
+def time_steps(fn, steps, sync, barrier=None):
+    """Exactly `steps` calls of fn between two events on the current stream; returns ms total."""
+    if barrier:
+        barrier()
+    sync()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    sync()
+    if barrier:
+        barrier()
+    return start.elapsed_time(end)
+
+
+def flush_l2(buf):
+    buf.add_(1)
+
+
+def secondary_shapes(gk, peaks, device):
+    """Other BASELINE shapes, reported beside the headline (short runs; L2 flushed between
+    iterations by writing a 512 MiB buffer, since several of these fit in the 126 MB L2)."""
+    out = []
+    scratch = torch.zeros(512 * 1024 * 1024 // 4, dtype=torch.int32, device=device)
+    cases = [
+        ("cfg1 1024^3 bf16", 1024, 1024, 1024, torch.bfloat16, 0, None, None, "tensor"),
+        ("cfg2 4096^3 bf16", 4096, 4096, 4096, torch.bfloat16, 1, None, None, "tensor"),
+        ("cfg2 4096^3 fp16", 4096, 4096, 4096, torch.float16, 1, None, None, "tensor"),
+        ("cfg2 8192^3 fp16", 8192, 8192, 8192, torch.float16, 1, None, None, "tensor"),
+        ("cfg3 8192x14336x4096 bf16", 8192, 14336, 4096, torch.bfloat16, 2, 1.0, 0.02, "tensor"),
+        ("cfg3 8192x4096x14336 bf16", 8192, 4096, 14336, torch.bfloat16, 2, 1.0, 0.02, "tensor"),
+        ("cfg4 16x28672x8192 bf16", 16, 28672, 8192, torch.bfloat16, 3, 1.0, 0.02, "hbm"),
+        ("cfg4 64x28672x8192 bf16", 64, 28672, 8192, torch.bfloat16, 3, 1.0, 0.02, "hbm"),
+        ("cfg4 128x28672x8192 bf16", 128, 28672, 8192, torch.bfloat16, 3, 1.0, 0.02, "hbm"),
+    ]
+    for name, M, N, K, dtype, seed, sa, sb, bound in cases:
+        A, B = device_inputs(M, N, K, seed, dtype, device, sa, sb)
+        C = torch.empty((M, N), dtype=dtype, device=device)
+        for _ in range(3):
+            gk.gemm_tn_test(A, B, C)
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(10):
+            flush_l2(scratch)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            gk.gemm_tn_test(A, B, C)
+            e.record()
+            e.synchronize()
+            times.append(s.elapsed_time(e))
+        ms = statistics.median(times)
+        tf = gemm_flops(M, N, K) / ms / 1e9
+        gbs = gemm_bytes(M, N, K) / ms / 1e6
+        rec = {"shape": name, "ms": round(ms, 4), "tflops": round(tf, 1), "gbs": round(gbs, 1), "bound": bound}
+        if bound == "tensor":
+            rec["frac"] = round(tf / peaks["bf16_tflops"], 4)
+        else:
+            rec["frac"] = round(gbs / peaks["hbm_gbs"], 4)
+        out.append(rec)
+        del A, B, C
+    gk.device_status()
+    return out
+
+
+def cpu_baseline_sample(M, N, K, seed, rows, target_seconds=10.0):
+    """Times the CPU oracle on `rows` rows of A against all of B (same distributions)."""
+    from oracle import oracle
+
+    A, B = oracle.make_inputs(rows, N, K, seed, torch.bfloat16)
+    sec, threads, _ = oracle.time_cpu_matmul(A, B, min_seconds=target_seconds, max_runs=5)
+    tf = gemm_flops(rows, N, K) / sec / 1e12
+    return {"value": round(tf, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"torch fp32 matmul (the reference's check expression) of {rows} rows of A "
+                      f"x all of B, N={N} K={K}; {sec:.3f} s per call; host has {os.cpu_count()} logical cores"}
+
+
+# --------------------------------------------------------------- reference ---
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    from oracle import oracle
+
+    if args.gpus == 1:
+        M = N = K = 8192
+        seed, workload = 1, "cfg2 square bf16 GEMM M=N=K=8192"
+    else:
+        M = N = K = 32768
+        seed, workload = 4, f"cfg5 bf16 GEMM M=N=K=32768, N-split over {args.gpus} GPUs + all-gather of C"
+    rows = 1024 if args.gpus == 1 else 64
+    A, B = oracle.make_inputs(rows, N, K, seed, torch.bfloat16)
+    for _ in range(min(args.warmup, 2)):
+        oracle.reference_matmul_fp32(A, B)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.reference_matmul_fp32(A, B)
+    sec = (time.perf_counter() - t0) / args.steps
+    tf = gemm_flops(rows, N, K) / sec / 1e12
+    sample = (f"each step = torch fp32 matmul of a {rows}-row slab of A x all of B (N={N}, K={K}); "
+              f"TFLOP/s of the slab stands for the whole GEMM")
+    line = {
+        "impl": "reference", "metric": "bf16 GEMM TFLOP/s", "value": round(tf, 4), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": workload, "sample_rows": rows},
+        "cpu_baseline": {"value": round(tf, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": round(tf, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# -------------------------------------------------------------------- ours ---
+def run_single(args):
+    import gemm_kernels as gk
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_src = load_peaks()
+    M = N = K = 8192
+    dtype = torch.bfloat16
+    A, B = device_inputs(M, N, K, 1, dtype, device)
+    C = torch.empty((M, N), dtype=dtype, device=device)
+    step = lambda: gk.gemm_tn_test(A, B, C)  # noqa: E731
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clk:
+        ms_total = time_steps(step, args.steps, torch.cuda.synchronize)
+    gk.device_status()
+    ms = ms_total / args.steps
+    tflops = gemm_flops(M, N, K) / ms / 1e9
+
+    # end to end: pinned host operands in, host result out, every step
+    Ah, Bh = A.cpu().pin_memory(), B.cpu().pin_memory()
+    Ch = torch.empty((M, N), dtype=dtype).pin_memory()
+    Ad, Bd, Cd = torch.empty_like(A), torch.empty_like(B), torch.empty_like(C)
+
+    def e2e_step():
+        Ad.copy_(Ah, non_blocking=True)
+        Bd.copy_(Bh, non_blocking=True)
+        gk.gemm_tn_test(Ad, Bd, Cd)
+        Ch.copy_(Cd, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = time_steps(e2e_step, e2e_steps, torch.cuda.synchronize) / e2e_steps
+    gk.device_status()
+    e2e_tflops = gemm_flops(M, N, K) / e2e_ms / 1e9
+    del Ad, Bd, Cd
+
+    shapes = [] if args.no_shapes else secondary_shapes(gk, peaks, device)
+    cpu = None if args.no_cpu else cpu_baseline_sample(M, N, K, 1, rows=2048)
+
+    timed_s = ms_total / 1e3
+    peak_key = "bf16_tflops" if timed_s <= 1.0 else "bf16_tflops_sustained"
+    peak = float(peaks.get(peak_key) or peaks["bf16_tflops"])
+    line = {
+        "metric": "bf16 GEMM TFLOP/s", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "cfg2 square bf16 TN GEMM M=N=K=8192, fp32 accumulate, bf16 out, seed 1",
+                   "M": M, "N": N, "K": K, "tile_config": gk.describe_config(gk.select_config(M, N, K, 0)),
+                   "l2": "operands 256 MiB > 126 MB L2 (inputs larger than L2; no flush between steps)"},
+        "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(tflops / peak, 4), "traffic": None,
+                     "peak_source": f"{peak_src}:{peak_key}", "kernel": "gemm_sm100::gemm_tn_kernel",
+                     "flops_per_launch": gemm_flops(M, N, K)},
+        "cpu_baseline": cpu,
+        "shapes": shapes,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_multi(args):
+    import torch.distributed as dist
+
+    import gemm_kernels as gk
+
+    rank = int(os.environ["RANK"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    world = int(os.environ["WORLD_SIZE"])
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", device_id=device)
+    peaks, peak_src = load_peaks()
+    M = N = K = 32768
+    dtype = torch.bfloat16
+    lo, hi = gk.shard_rows(N, world, rank)
+    g = torch.Generator(device=device).manual_seed(4)          # same A on every rank
+    A = (torch.randn((M, K), generator=g, device=device, dtype=torch.float32) / K ** 0.5).to(dtype)
+    gb = torch.Generator(device=device).manual_seed(4000 + rank)
+    B_shard = (torch.randn((hi - lo, K), generator=gb, device=device, dtype=torch.float32) / K ** 0.5).to(dtype)
+    C = torch.empty((M, N), dtype=dtype, device=device)
+    plan = gk.NSplitPlan.create(M, N, world, dtype, device, num_panels=args.panels)
+    step = lambda: gk.gemm_tn_nsplit(A, B_shard, C, plan=plan)  # noqa: E731
+
+    def barrier():
+        dist.barrier(device_ids=[local])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clk:
+        ms_total = time_steps(step, args.steps, torch.cuda.synchronize, barrier)
+    gk.device_status()
+    t = torch.tensor([ms_total], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    tflops = gemm_flops(M, N, K) / ms / 1e9
+
+    # end to end: host A and B shard in, host C out, each step
+    Ah, Bh = A.cpu().pin_memory(), B_shard.cpu().pin_memory()
+    Ch = torch.empty((M, N), dtype=dtype).pin_memory()
+
+    def e2e_step():
+        A.copy_(Ah, non_blocking=True)
+        B_shard.copy_(Bh, non_blocking=True)
+        gk.gemm_tn_nsplit(A, B_shard, C, plan=plan)
+        Ch.copy_(C, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 3))
+    e2e_step()
+    torch.cuda.synchronize()
+    e2e_total = time_steps(e2e_step, e2e_steps, torch.cuda.synchronize, barrier)
+    t = torch.tensor([e2e_total], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = t.item() / e2e_steps
+    gk.device_status()
+
+    if rank == 0:
+        per_gpu = tflops / world
+        peak = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"])
+        line = {
+            "metric": "bf16 GEMM TFLOP/s", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"cfg5 bf16 TN GEMM M=N=K=32768, B row-sharded over {world} GPUs, "
+                                   f"NCCL all-gather of C, {plan.num_panels} row panels", "M": M, "N": N, "K": K,
+                       "per_gpu_tflops": round(per_gpu, 2),
+                       "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"},
+            "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (M * K + (hi - lo) * K) * 2, "d2h_bytes_per_step": M * N * 2,
+                    "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+            "gpu_launches": args.steps * plan.num_panels,
+            "clocks": clk.summary(),
+            "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": peak, "unit": "TFLOP/s",
+                         "frac": round(per_gpu / peak, 4), "traffic": None,
+                         "peak_source": f"{peak_src}:bf16_tflops_sustained", "kernel": "gemm_sm100::gemm_tn_kernel",
+                         "note": "per-GPU TFLOP/s of the whole step (GEMM panels + overlapped all-gather)"},
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier(device_ids=[local])
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--panels", type=int, default=8)
+    ap.add_argument("--no-shapes", action="store_true", help="skip the secondary BASELINE shapes")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        args.steps = args.steps or 5
+        args.warmup = 1 if args.warmup is None else args.warmup
+        run_reference(args, rank)
+        return
+    if world > 1 or args.gpus > 1:
+        if world == 1:
+            raise SystemExit("multi-GPU runs are launched with: python -m torch.distributed.run --nnodes=1 "
+                             "--nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N")
+        args.steps = args.steps or 5
+        args.warmup = 3 if args.warmup is None else args.warmup
+        run_multi(args)
+    else:
+        args.steps = args.steps or 200
+        args.warmup = 5 if args.warmup is None else args.warmup
+        run_single(args)
+
+
+if __name__ == "__main__":
+    main()

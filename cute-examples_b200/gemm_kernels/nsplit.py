@@ -107,8 +107,7 @@ def gemm_tn_nsplit(A: torch.Tensor, B_shard: torch.Tensor, C: torch.Tensor,
         rows = r1 - r0
         slot = p & 1
         stage = plan.staging[slot][:rows]
-        gath = plan.gathered[slot][:, :rows] if rows == plan.panel_rows else \
-            plan.gathered[slot].view(-1)[: world * rows * per].view(world, rows, per)
+        gath = plan.gathered[slot].view(-1)[: world * rows * per].view(world, rows, per)
         if on_gpu and done_events[slot] is not None:
             compute.wait_event(done_events[slot])
         local_gemm(A[r0:r1], B_shard, stage)
@@ -117,13 +116,13 @@ def gemm_tn_nsplit(A: torch.Tensor, B_shard: torch.Tensor, C: torch.Tensor,
             ready.record(compute)
             comm.wait_event(ready)
             with torch.cuda.stream(comm):
-                dist.all_gather_into_tensor(gath, stage, group=group)
+                dist.all_gather_into_tensor(gath.view(world * rows, per), stage, group=group)
                 C[r0:r1].view(rows, world, per).copy_(gath.permute(1, 0, 2))
                 ev = torch.cuda.Event()
                 ev.record(comm)
             done_events[slot] = ev
         else:
-            dist.all_gather_into_tensor(gath, stage.contiguous(), group=group)
+            dist.all_gather_into_tensor(gath.view(world * rows, per), stage.contiguous(), group=group)
             C[r0:r1].view(rows, world, per).copy_(gath.permute(1, 0, 2))
     if on_gpu:
         compute.wait_stream(comm)

@@ -1,0 +1,90 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and
+rejects bad arguments before touching CUDA."""
+import ctypes
+import re
+
+import pytest
+import torch
+
+from conftest import HEADER, LIB_PATH, load_capi
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(gemm_sm100_\w+)\s*\(", text)))
+
+
+def test_library_is_built():
+    assert LIB_PATH.exists(), "build with: python cute-examples_b200/build_native.py"
+
+
+def test_every_declared_symbol_is_exported(capi):
+    names = declared_symbols()
+    assert "gemm_sm100_tn" in names and len(names) >= 8
+    for n in names:
+        assert hasattr(capi, n), f"{n} declared in include/gemm_sm100.h but not exported"
+
+
+def test_error_strings(capi):
+    for code in range(0, 10):
+        s = capi.gemm_sm100_error_string(code)
+        assert s and s != b"unknown error code"
+    assert capi.gemm_sm100_error_string(12345) == b"unknown error code"
+
+
+def test_describe_and_options(capi):
+    buf = ctypes.create_string_buffer(256)
+    n = 0
+    while capi.gemm_sm100_describe_config(n, buf, 256) == 0:
+        assert b"tile=" in buf.value and b"stages=" in buf.value
+        n += 1
+    assert n >= 4
+    assert capi.gemm_sm100_set_option(b"tile_config", n) == 9
+    assert capi.gemm_sm100_set_option(b"tile_config", -1) == 0
+    assert capi.gemm_sm100_set_option(b"timeout_ms", 0) == 9
+    assert capi.gemm_sm100_set_option(b"timeout_ms", 2000) == 0
+    assert capi.gemm_sm100_set_option(b"no_such_option", 1) == 9
+    assert capi.gemm_sm100_set_option(None, 1) == 1
+
+
+BAD = [
+    # M, N, K, lda, ldb, ldc, dtype, a, b, c, expected
+    (-1, 8, 8, 8, 8, 8, 0, 256, 512, 1024, 2),       # negative extent
+    (8, 8, 8, 8, 8, 8, 7, 256, 512, 1024, 4),        # dtype
+    (8, 8, 12, 16, 16, 8, 0, 256, 512, 1024, 2),     # K % 8
+    (8, 8, 16, 8, 16, 8, 0, 256, 512, 1024, 2),      # lda < K
+    (8, 16, 16, 16, 16, 8, 0, 256, 512, 1024, 2),    # ldc < N
+    (8, 8, 16, 20, 16, 8, 0, 256, 512, 1024, 3),     # lda % 8
+    (8, 8, 16, 16, 16, 8, 0, 260, 512, 1024, 3),     # A misaligned
+    (8, 8, 16, 16, 16, 8, 0, 256, 512, 1028, 3),     # C misaligned
+    (8, 8, 16, 16, 16, 8, 0, 0, 512, 1024, 1),       # null A
+    (8, 8, 16, 16, 16, 8, 0, 256, 512, 0, 1),        # null C
+]
+
+
+@pytest.mark.parametrize("case", BAD)
+def test_bad_arguments_are_rejected_on_the_host(capi, case):
+    M, N, K, lda, ldb, ldc, dtype, a, b, c, want = case
+    err = ctypes.c_int(-7)
+    rc = capi.gemm_sm100_tn(a or None, b or None, c or None, M, N, K, lda, ldb, ldc, dtype, None, 0, None,
+                            ctypes.byref(err))
+    assert rc == want
+    assert err.value == 0
+
+
+def test_empty_problem_is_a_noop(capi):
+    err = ctypes.c_int(0)
+    assert capi.gemm_sm100_tn(None, None, None, 0, 8, 8, 8, 8, 8, 0, None, 0, None, ctypes.byref(err)) == 0
+    assert capi.gemm_sm100_tn(None, None, None, 8, 0, 8, 8, 8, 8, 0, None, 0, None, ctypes.byref(err)) == 0
+
+
+def test_binding_rejects_bad_tensors_with_runtime_error():
+    import gemm_kernels as gk
+
+    z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt)  # noqa: E731
+    with pytest.raises(RuntimeError, match="CUDA tensors"):
+        gk.gemm_tn_test(z(8, 8), z(8, 8), z(8, 8))
+    assert gk.gemm_tn_test is gk._C.gemm_tn_test
+    # keyword names of the reference binding
+    with pytest.raises(RuntimeError):
+        gk.gemm_tn_test(A=z(8, 8), B=z(8, 8), C=z(8, 8))

@@ -1,0 +1,274 @@
+"""Parity tests proper: the CUDA path, called through the C ABI (ctypes on raw device pointers)
+and through the PyTorch binding, against the CPU oracle, the golden fixtures generated from
+the reference's check, and exact known-answer cases.
+
+Tolerances (written here, as the acceptance metric states them):
+    max|C - C_ref| / max|C_ref|  <= 2e-2 for bf16 output, <= 5e-3 for fp16 output,
+plus the reference's own  allclose(atol=1e-2, rtol=1e-2)  (kernels/tests/gemm_test.py:10)
+where its operands are O(1) (for 1/sqrt(K)-scaled operands it is implied by the first).
+Known-answer cases (entries in {-1,0,1}, identity, one-hot) must match BITWISE.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import capi_gemm, capi_status
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+DT = {0: torch.bfloat16, 1: torch.float16}
+NUM_CONFIGS = 4
+
+
+@pytest.fixture(scope="module")
+def gk():
+    import gemm_kernels
+
+    gemm_kernels.set_option("tile_config", -1)
+    gemm_kernels.set_option("max_ctas", 0)
+    return gemm_kernels
+
+
+@pytest.fixture(autouse=True)
+def _reset_options(capi):
+    yield
+    capi.gemm_sm100_set_option(b"tile_config", -1)
+    capi.gemm_sm100_set_option(b"max_ctas", 0)
+
+
+def run_capi(capi, A, B, prefill=float("nan")):
+    Ad, Bd = A.cuda(), B.cuda()
+    C = torch.full((A.shape[0], B.shape[0]), prefill, dtype=A.dtype, device="cuda")
+    assert capi_gemm(capi, Ad, Bd, C) == 0
+    rc, word = capi_status(capi)
+    assert (rc, word) == (0, 0), f"device status rc={rc} word={word:#x}"
+    return C.cpu()
+
+
+def assert_close(C, C_ref, dtype, also_reference_check=False):
+    assert not torch.isnan(C.float()).any(), "output holds NaN: some element was never written"
+    err = oracle.normalized_max_error(C, C_ref)
+    assert err <= oracle.tolerance(dtype), f"normalised max error {err:.3e}"
+    if also_reference_check:
+        assert oracle.measure_error_stats(C.float(), C_ref)[2]
+
+
+# ------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("name", ["small_bf16", "ragged_bf16", "small_fp16", "ternary_bf16", "ternary_fp16"])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3])
+def test_golden_cases(capi, golden, name, config):
+    M, N, K, seed, code, ternary = (int(x) for x in golden[f"{name}/meta"])
+    dtype = DT[code]
+    A = torch.from_numpy(golden[f"{name}/A"].view(np.int16)).view(dtype)
+    B = torch.from_numpy(golden[f"{name}/B"].view(np.int16)).view(dtype)
+    C_ref = torch.from_numpy(golden[f"{name}/C_ref"])
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = run_capi(capi, A, B)
+    if ternary:
+        assert torch.equal(C.view(torch.int16), C_ref.to(dtype).view(torch.int16))
+    else:
+        assert_close(C, C_ref, dtype, also_reference_check=True)
+
+
+def test_config1_1024_cubed(capi, gk, golden):
+    """BASELINE config 1: M=N=K=1024, seed 0, bf16; whole matrix against both oracles, sampled
+    rows against the fixture, through both call paths."""
+    A, B = oracle.make_inputs(1024, 1024, 1024, 0, torch.bfloat16)
+    C_ref = oracle.reference_matmul_fp32(A, B)
+    C = run_capi(capi, A, B)
+    assert_close(C, C_ref, torch.bfloat16, also_reference_check=True)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    rows = [int(r) for r in golden["cfg1/rows"]]
+    assert_close(C[rows], torch.from_numpy(golden["cfg1/C_ref_rows"]), torch.bfloat16)
+    C2 = torch.full((1024, 1024), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = gk.gemm_tn_test(A.cuda(), B.cuda(), C2)
+    assert out.data_ptr() == C2.data_ptr()           # returns the caller's tensor
+    gk.device_status()
+    assert torch.equal(C2.cpu().view(torch.int16), C.view(torch.int16))   # both paths, same bits
+
+
+# ----------------------------------------------------------- known answers
+@pytest.mark.parametrize("config", range(NUM_CONFIGS))
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_identity_b_returns_a_bitwise(capi, config, dtype):
+    """B = I  =>  C == A bit for bit: any transposition, swizzle or descriptor slip shows."""
+    M, K = 384, 512
+    A, _ = oracle.make_inputs(M, K, K, 31, dtype, a_std=1.0)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = run_capi(capi, A, torch.eye(K, dtype=dtype))
+    assert torch.equal(C.view(torch.int16), A.view(torch.int16))
+
+
+@pytest.mark.parametrize("config", range(NUM_CONFIGS))
+def test_ternary_nonsquare_exact(capi, config):
+    """M != N != K with integer-valued sums: exact, and TN-vs-NN confusion cannot cancel."""
+    M, N, K = 640, 896, 256
+    A, B = oracle.make_ternary_inputs(M, N, K, 32)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = run_capi(capi, A, B)
+    want = oracle.c_gemm_tn(A, B)
+    assert torch.equal(C.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("config", range(NUM_CONFIGS))
+def test_one_hot_localises_tiles(capi, config):
+    """A[m, k_m] = 1 and B[n, k] = k-dependent pattern: C[m, n] = B[n, k_m]; a wrong tile
+    coordinate moves a whole block."""
+    M, N, K = 512, 768, 256
+    ks = (torch.arange(M) * 7) % K
+    A = torch.zeros(M, K, dtype=torch.bfloat16)
+    A[torch.arange(M), ks] = 1.0
+    B = ((torch.arange(N).view(N, 1) * 3 + torch.arange(K).view(1, K)) % 251).to(torch.bfloat16)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = run_capi(capi, A, B)
+    want = B[:, ks].T.contiguous()
+    assert torch.equal(C.view(torch.int16), want.view(torch.int16))
+
+
+# --------------------------------------------------------------- edge shapes
+EDGE_SHAPES = [
+    (16, 256, 64), (64, 256, 128), (128, 512, 64), (144, 256, 192), (256, 256, 64),
+    (1, 8, 8), (8, 8, 8), (129, 8, 8), (257, 264, 72), (100, 1000, 1000), (300, 520, 2056),
+    (128, 28672 // 8, 1024),
+]
+
+
+@pytest.mark.parametrize("shape", EDGE_SHAPES)
+@pytest.mark.parametrize("config", [-1, 0, 2])
+def test_edge_shapes(capi, shape, config):
+    M, N, K = shape
+    A, B = oracle.make_inputs(M, N, K, 40 + M % 7)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+def test_empty_and_k0(capi):
+    C = torch.full((4, 8), 3.0, dtype=torch.bfloat16, device="cuda")
+    A = torch.empty((4, 0), dtype=torch.bfloat16, device="cuda")
+    B = torch.empty((8, 0), dtype=torch.bfloat16, device="cuda")
+    err = ctypes.c_int(0)
+    rc = capi.gemm_sm100_tn(None, None, C.data_ptr(), 4, 8, 0, 0, 0, 8, 0, None, 0, None, ctypes.byref(err))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(C.cpu(), torch.zeros(4, 8, dtype=torch.bfloat16))     # K = 0: C = 0
+    assert capi_gemm(capi, A[:0], B, C[:0]) == 0                               # M = 0: no-op
+
+
+# ---------------------------------------------------------- bounds / strides
+@pytest.mark.parametrize("config", range(NUM_CONFIGS))
+@pytest.mark.parametrize("shape", [(200, 264, 128), (384, 512, 64)])
+def test_guard_bands_and_strided_c(capi, config, shape):
+    """C lives inside a larger sentinel-filled buffer with ldc > N: every element of C is
+    overwritten, nothing outside it is touched."""
+    M, N, K = shape
+    pad_rows, ldc = 8, N + 64
+    A, B = oracle.make_inputs(M, N, K, 50)
+    sentinel = -12345.0
+    buf = torch.full((M + 2 * pad_rows, ldc), sentinel, dtype=torch.bfloat16, device="cuda")
+    C = buf[pad_rows:pad_rows + M, 32:32 + N]
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    assert capi_gemm(capi, A.cuda(), B.cuda(), C, ldc=ldc) == 0
+    assert capi_status(capi) == (0, 0)
+    host = buf.cpu()
+    inner = host[pad_rows:pad_rows + M, 32:32 + N].clone()
+    assert_close(inner, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    host[pad_rows:pad_rows + M, 32:32 + N] = sentinel
+    assert torch.all(host == sentinel), "kernel wrote outside C"
+
+
+def test_binding_accepts_strided_c_view(gk):
+    M, N, K = 256, 256, 128
+    A, B = oracle.make_inputs(M, N, K, 51)
+    big = torch.zeros((M, 2 * N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A.cuda(), B.cuda(), big[:, N:])
+    gk.device_status()
+    assert torch.all(big[:, :N] == 0)
+    assert_close(big[:, N:].cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+# ------------------------------------------- persistence / determinism / reuse
+@pytest.mark.parametrize("config,max_ctas", [(0, 2), (0, 6), (1, 4), (2, 1), (2, 3), (3, 5)])
+def test_many_tiles_per_cta(capi, config, max_ctas):
+    """Few CTAs, many tiles each: the accumulator buffers alternate and are reused, the smem
+    ring wraps many times; a stale accumulator or a phase slip cannot hide."""
+    M, N, K = 1024, 1536, 320
+    A, B = oracle.make_inputs(M, N, K, 60)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    At, Bt = oracle.make_ternary_inputs(M, N, 256, 61)
+    Ct = run_capi(capi, At, Bt)
+    assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+def test_deterministic(capi):
+    A, B = oracle.make_inputs(2048, 2048, 1024, 62)
+    C1 = run_capi(capi, A, B)
+    C2 = run_capi(capi, A, B)
+    assert torch.equal(C1.view(torch.int16), C2.view(torch.int16))
+
+
+def test_runs_on_a_side_stream(gk):
+    A, B = oracle.make_inputs(512, 512, 256, 63)
+    s = torch.cuda.Stream()
+    C = torch.full((512, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+    Ad, Bd = A.cuda(), B.cuda()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        gk.gemm_tn_test(Ad, Bd, C)
+    s.synchronize()
+    assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+# ------------------------------------------------ BASELINE configs 2-4 (1 GPU)
+def sampled_check(gk, M, N, K, seed, dtype, a_std, b_std, n_rows=192):
+    """Full-size run; the CPU oracle is evaluated on a random sample of rows of A (complete
+    rows of C), which pins every column tile and K-block at these sizes."""
+    A, B = oracle.make_inputs(M, N, K, seed, dtype, a_std=a_std, b_std=b_std)
+    C = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+    gk.gemm_tn_test(A.cuda(), B.cuda(), C)
+    gk.device_status()
+    assert not torch.isnan(C).any().item()
+    g = torch.Generator().manual_seed(seed + 1000)
+    rows = torch.randperm(M, generator=g)[: min(n_rows, M)].sort().values
+    rows = torch.unique(torch.cat([rows, torch.tensor([0, M - 1])]))
+    C_ref = oracle.reference_matmul_fp32(A[rows], B)
+    got = C[rows.cuda()].cpu()
+    err = oracle.normalized_max_error(got, C_ref)
+    assert err <= oracle.tolerance(dtype), f"normalised max error {err:.3e}"
+    return err
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_config2_square(gk, n, dtype):
+    sampled_check(gk, n, n, n, 1, dtype, None, None)
+
+
+@pytest.mark.parametrize("shape", [(8192, 14336, 4096), (8192, 4096, 14336)])
+def test_config3_mlp(gk, shape):
+    M, N, K = shape
+    sampled_check(gk, M, N, K, 2, torch.bfloat16, 1.0, 0.02)
+
+
+@pytest.mark.parametrize("M", [16, 64, 128])
+def test_config4_skinny(gk, M):
+    sampled_check(gk, M, 28672, 8192, 3, torch.bfloat16, 1.0, 0.02)
+
+
+def test_full_size_identity_property(gk):
+    """Size-independent property at a full BASELINE size: with B = I (8192 x 8192) the output
+    must reproduce A bit for bit."""
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(7)
+    A = torch.randn((n, n), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    eye = torch.eye(n, dtype=torch.bfloat16, device="cuda")
+    C = torch.full((n, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A, eye, C)
+    gk.device_status()
+    assert torch.equal(C.view(torch.int16), A.view(torch.int16))
