@@ -27,16 +27,19 @@ using namespace gemm_sm100;
 __device__ unsigned int g_status_word;
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 4;
+constexpr int kNumConfigs = 7;
 
 struct ConfigInfo {
-  int cta_group, block_n, stages;
+  int cta_group, mma_n, halves, stages, epi_warps;
 };
 constexpr ConfigInfo kConfigs[kNumConfigs] = {
-    {2, 256, 6},
-    {2, 128, 8},
-    {1, 256, 4},
-    {1, 128, 6},
+    {2, 256, 1, 6, 4},   // 256 x 256 pair tile, alternating accumulator slots
+    {2, 256, 2, 4, 8},   // 256 x 512 pair tile, both slots, 8 epilogue warps
+    {1, 256, 1, 4, 4},   // 128 x 256 single-CTA tile
+    {1, 128, 1, 6, 4},   // 128 x 128 single-CTA tile
+    {2, 256, 2, 4, 4},
+    {2, 256, 1, 6, 8},
+    {1, 256, 1, 4, 8},
 };
 
 struct DeviceState {
@@ -53,6 +56,10 @@ DeviceState g_dev[kMaxDevices];
 long g_opt_tile_config = -1;
 long g_opt_timeout_ms = 2000;
 long g_opt_max_ctas = 0;
+long g_opt_debug_flags = 0;
+long g_opt_group_m = 0;
+unsigned long long* g_trace_ptr = nullptr;   // device buffer for per-CTA trace records, or null
+size_t g_trace_bytes = 0;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -144,24 +151,24 @@ int validate(const Problem& p) {
 
 inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 
-// Cost model used to choose a tile configuration: time ~ waves x (work of one tile),
-// where a wave is one tile on every resident CTA pair.  Narrow tiles pay a little more
-// shared-memory traffic per flop, single-CTA tiles twice the B traffic.
+// Cost model used to choose a tile configuration: time ~ waves x (per-CTA work of one tile) /
+// (relative rate of the configuration), where a wave is one tile on every resident CTA (pair).
+// Rates are measured on B200 at 8192^3 (power-capped steady state), relative to the 256 x 512
+// pair tile: the wider the tile, the fewer bytes reach shared memory per flop.
+constexpr int kAutoConfigs = 4;                       // candidates of the automatic choice
+constexpr double kConfigRate[kAutoConfigs] = {0.87, 1.0, 0.72, 0.55};
+
 int choose_config(const Problem& p, int sm_count) {
   if (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) return static_cast<int>(g_opt_tile_config);
   double best = 1e300;
   int best_i = 0;
-  for (int i = 0; i < kNumConfigs; ++i) {
+  for (int i = 0; i < kAutoConfigs; ++i) {
     const ConfigInfo& c = kConfigs[i];
-    const long tiles = ceil_div(p.M, 128L * c.cta_group) * ceil_div(p.N, c.block_n);
+    const int block_n = c.mma_n * c.halves;
+    const long tiles = ceil_div(p.M, 128L * c.cta_group) * ceil_div(p.N, block_n);
     const long slots = sm_count / c.cta_group;
     const long waves = ceil_div(tiles, slots);
-    double tile_cost = static_cast<double>(c.block_n) / 256.0;   // per-CTA MMA time of one tile
-    // Measured on B200 (8192^3): a 128-wide tile moves 1.5x the shared-memory bytes per flop
-    // and runs at ~0.6x the rate of a 256-wide one; single-CTA tiles at ~0.82x of paired ones.
-    if (c.block_n == 128) tile_cost *= 1.7;
-    if (c.cta_group == 1) tile_cost *= 1.22;
-    const double cost = static_cast<double>(waves) * tile_cost;
+    const double cost = static_cast<double>(waves) * block_n / kConfigRate[i];
     if (cost < best) {
       best = cost;
       best_i = i;
@@ -173,15 +180,19 @@ int choose_config(const Problem& p, int sm_count) {
 template <int kCfgIndex, bool kIsBf16>
 int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
-  using Cfg = GemmConfig<ci.cta_group, ci.block_n, ci.stages, kIsBf16>;
-  auto kernel = gemm_tn_kernel<Cfg>;
+  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  // The instrumented instantiation runs only while a trace buffer or an experiment flag is set.
+  const bool debug = g_trace_ptr != nullptr || g_opt_debug_flags != 0;
+  auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
   constexpr int dt = kIsBf16 ? 0 : 1;
   cudaError_t e;
 
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!st.attr_set[kCfgIndex][dt]) {
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
       if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
       int max_ctas = st.sm_count;
       if (Cfg::kCtaGroup == 2) {
@@ -215,9 +226,11 @@ int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* c
   tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
   tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
   tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
-  tp.group_m = Cfg::kCtaGroup == 2 ? 8 : 16;
+  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : (Cfg::kCtaGroup == 2 ? 8 : 16);
   tp.status = st.status_ptr;
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
+  tp.trace = nullptr;
+  tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags);
 
   CUtensorMap map_a, map_b, map_c;
   int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
@@ -232,6 +245,9 @@ int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* c
   if (g_opt_max_ctas > 0 && g_opt_max_ctas < cap) cap = g_opt_max_ctas - g_opt_max_ctas % Cfg::kCtaGroup;
   if (cap < Cfg::kCtaGroup) cap = Cfg::kCtaGroup;
   if (ctas > cap) ctas = cap;
+
+  if (g_trace_ptr && g_trace_bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
+    tp.trace = g_trace_ptr;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
@@ -257,6 +273,9 @@ int dispatch(int config, const Problem& p, DeviceState& st, cudaStream_t stream,
     case 1: return launch_config<1, kIsBf16>(p, st, stream, cuda_error_out);
     case 2: return launch_config<2, kIsBf16>(p, st, stream, cuda_error_out);
     case 3: return launch_config<3, kIsBf16>(p, st, stream, cuda_error_out);
+    case 4: return launch_config<4, kIsBf16>(p, st, stream, cuda_error_out);
+    case 5: return launch_config<5, kIsBf16>(p, st, stream, cuda_error_out);
+    case 6: return launch_config<6, kIsBf16>(p, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }
@@ -345,6 +364,16 @@ int gemm_sm100_set_option(const char* name, long value) {
     g_opt_timeout_ms = value;
     return GEMM_SM100_OK;
   }
+  if (std::strcmp(name, "debug_flags") == 0) {
+    if (value < 0 || value > 7) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_debug_flags = value;
+    return GEMM_SM100_OK;
+  }
+  if (std::strcmp(name, "group_m") == 0) {
+    if (value < 0 || value > 4096) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_group_m = value;
+    return GEMM_SM100_OK;
+  }
   if (std::strcmp(name, "max_ctas") == 0) {
     if (value < 0) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_max_ctas = value;
@@ -353,12 +382,20 @@ int gemm_sm100_set_option(const char* name, long value) {
   return GEMM_SM100_ERR_BAD_OPTION;
 }
 
+int gemm_sm100_set_trace_buffer(void* device_buffer, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (device_buffer != nullptr && (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) return GEMM_SM100_ERR_BAD_ALIGNMENT;
+  g_trace_ptr = static_cast<unsigned long long*>(device_buffer);
+  g_trace_bytes = device_buffer ? bytes : 0;
+  return GEMM_SM100_OK;
+}
+
 int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes) {
   if (!buf || buf_bytes == 0) return GEMM_SM100_ERR_NULL_POINTER;
   if (index < 0 || index >= kNumConfigs) return GEMM_SM100_ERR_BAD_OPTION;
   const ConfigInfo& c = kConfigs[index];
-  std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d", c.cta_group,
-                128 * c.cta_group, c.block_n, c.stages, 2 * c.block_n);
+  std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d epilogue_warps=%d",
+                c.cta_group, 128 * c.cta_group, c.mma_n * c.halves, c.stages, 2 * c.mma_n, c.epi_warps);
   return GEMM_SM100_OK;
 }
 

@@ -9,10 +9,11 @@
 //   warp 0      TMA producer   : global -> smem ring of kStages (A tile + B tile), mbarrier tx-count
 //   warp 1      MMA issuer     : one thread issues tcgen05.mma from smem descriptors into TMEM;
 //                                 tcgen05.commit frees ring slots and publishes finished accumulators
-//   warps 2..5  epilogue       : tcgen05.ld TMEM -> registers -> 16-bit -> swizzled smem -> TMA store
-// Two accumulator buffers live in TMEM (2 x kBlockN fp32 columns), so the epilogue of
-// tile i runs under the mainloop of tile i+1 (the reference's single register-resident
-// accumulator idles the tensor pipe during every epilogue, gemm.cuh:368-395).
+//   warps 2..   epilogue       : tcgen05.ld TMEM -> registers -> 16-bit -> swizzled smem -> TMA store
+// Two accumulator slots live in TMEM (2 x kMmaN fp32 columns).  Either consecutive tiles
+// alternate between them, so the epilogue of tile i runs under the mainloop of tile i+1
+// (the reference's single register-resident accumulator idles the tensor pipe during every
+// epilogue, gemm.cuh:368-395), or one double-width tile owns both (see GemmConfig).
 //
 // kCtaGroup == 2 pairs two CTAs (a 2-CTA cluster) on one 256 x kBlockN tile: each CTA
 // loads its own 128 rows of A and its own kBlockN/2 rows of B with plain TMA loads, and
@@ -51,31 +52,71 @@ struct TileParams {
   int group_m;   // tiles along M per rasterisation group
   unsigned int* status;            // device word, 0 = ok
   unsigned long long timeout_ns;   // bound of every device-side wait
+  unsigned long long* trace;       // optional: kTraceWords counters per CTA (nullptr = off)
+  unsigned int debug_flags;        // experiments only; 0 in normal use (see kDebug*)
 };
 
-template <int kCtaGroup_, int kBlockN_, int kStages_, bool kIsBf16_>
+// Experiment switches (results are garbage with any of them set).
+enum : unsigned int {
+  kDebugSkipLoads = 1u,   // no TMA loads, MMA does not wait for operands: pure MMA issue/execute rate
+  kDebugSkipStores = 2u,  // epilogue reads TMEM but stores nothing
+  kDebugSkipMma = 4u,     // operands are loaded and released, no MMA is issued: pure load rate
+};
+
+// Per-CTA trace record (cycles are clock64 of the CTA's SM).
+enum : int {
+  kTraceEntry = 0,        // kernel entry
+  kTraceSetupDone = 1,    // barriers initialised, TMEM allocated
+  kTraceMmaFirst = 2,     // first operand stage landed
+  kTraceMmaStallFull = 3, // cycles the MMA thread waited for operand stages
+  kTraceMmaStallAcc = 4,  // cycles the MMA thread waited for a free accumulator
+  kTraceMmaEnd = 5,       // last MMA issued
+  kTraceProdStall = 6,    // cycles the producer waited for free ring slots
+  kTraceProdEnd = 7,      // last load issued
+  kTraceEpiStall = 8,     // cycles epilogue warp 2 waited for accumulators
+  kTraceEpiEnd = 9,       // epilogue warp 2 done
+  kTraceExit = 10,        // after tear-down barrier
+  kTraceTiles = 11,       // tiles this CTA processed
+  kTraceTimeEntryNs = 12, // %globaltimer at entry
+  kTraceTimeExitNs = 13,  // %globaltimer at exit
+  kTraceWords = 16,
+};
+
+template <int kCtaGroup_, int kMmaN_, int kHalves_, int kStages_, int kEpiWarps_, bool kIsBf16_>
 struct GemmConfig {
   static constexpr int kCtaGroup = kCtaGroup_;
   static constexpr int kBlockM = 128;              // rows of A (and of the accumulator) per CTA
-  static constexpr int kBlockN = kBlockN_;         // MMA N: columns of C per tile (whole pair)
+  static constexpr int kMmaN = kMmaN_;             // N of one MMA instruction (whole pair)
+  // kHalves == 1: the tile is kMmaN wide and the two accumulator slots in TMEM alternate
+  //               between consecutive tiles (the epilogue of one runs under the next mainloop).
+  // kHalves == 2: the tile is 2 x kMmaN wide and occupies both slots; every A stage feeds two
+  //               MMAs, so shared memory receives 25 % fewer bytes per flop, at the price of
+  //               an epilogue that is only partly hidden.
+  static constexpr int kHalves = kHalves_;
+  static constexpr int kBlockN = kMmaN * kHalves;  // columns of C per tile (whole pair)
   static constexpr int kBlockK = 64;               // 64 x 16 bit = one 128-byte swizzle row
   static constexpr int kStages = kStages_;
+  static constexpr int kEpiWarps = kEpiWarps_;     // 4 or 8
   static constexpr bool kIsBf16 = kIsBf16_;
   static constexpr int kUmmaK = 16;
-  static constexpr int kBRows = kBlockN / kCtaGroup;            // rows of B this CTA loads
+  static constexpr int kBRows = kMmaN / kCtaGroup;              // rows of B this CTA loads per half
   static constexpr int kABytes = kBlockM * kBlockK * 2;
-  static constexpr int kBBytes = kBRows * kBlockK * 2;
+  static constexpr int kBHalfBytes = kBRows * kBlockK * 2;
+  static constexpr int kBBytes = kHalves * kBHalfBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiCols = 64;                           // columns per TMA-store chunk
   static constexpr int kEpiWarpBuf = 32 * kEpiCols * 2;         // one warp, one chunk: 4 KiB
-  static constexpr int kEpiBytes = 4 * 2 * kEpiWarpBuf;         // 4 warps, double buffered
-  static constexpr int kTmemCols = 2 * kBlockN;                 // two accumulator buffers
+  static constexpr int kEpiBufs = 8 / kEpiWarps;                // staging buffers per warp
+  static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiWarpBuf;   // 32 KiB
+  static constexpr int kTmemCols = 2 * kMmaN;                   // two accumulator slots
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kBarrierBytes;
-  static constexpr int kThreads = 192;
-  static_assert(kBlockN % 64 == 0 && kBlockN >= 64 && kBlockN <= 256, "tile N");
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static_assert(kHalves == 1 || kHalves == 2, "halves");
+  static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps");
+  static_assert(kMmaN % 64 == 0 && kMmaN >= 64 && kMmaN <= 256, "MMA N");
   static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns: power of two");
-  static_assert(kBBytes % 1024 == 0, "B tile must keep 1024-byte swizzle alignment");
+  static_assert(kBHalfBytes % 1024 == 0, "B tile must keep 1024-byte swizzle alignment");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
@@ -86,26 +127,41 @@ struct WaitCtx {
   unsigned long long timeout_ns;
 };
 
-// Bounded mbarrier wait.  Returns false if the CTA was flagged or the wait ran out.
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                             uint32_t code) {
-#pragma unroll 1
-  for (int i = 0; i < 64; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+// Every wait below is executed by a whole, converged warp and returns a warp-uniform result:
+// the single-issuer roles keep all their values in uniform registers that way (TMA and MMA
+// instructions take uniform operands; a loop run by one diverged lane pays a register move
+// per operand).
+//
+// Cold path of a bounded mbarrier wait: polls until the phase completes, the CTA is flagged,
+// or the time limit passes (then flags this CTA and its pair peer and records `code`).
+__device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx, uint32_t code) {
+  bool done = false;
+  // try_wait suspends the thread for a hardware-defined while; normal waits end inside this
+  // first batch, without a read of the (slow) global timer.
+  if (__all_sync(0xffffffffu, mbar_wait_spin(bar, parity, 1024))) return true;
   const uint64_t t0 = global_timer_ns();
 #pragma unroll 1
   while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*ctx.abort_flag != 0) return false;
-    if (global_timer_ns() - t0 > ctx.timeout_ns) {
-      *ctx.abort_flag = 1;
-      st_cluster_u32(ctx.peer_abort_addr, 1);
-      atomicCAS(ctx.status, 0u, code);
+    done = __all_sync(0xffffffffu, mbar_wait_spin(bar, parity, 64));
+    if (done) return true;
+    const bool flagged = *ctx.abort_flag != 0;
+    const bool late = global_timer_ns() - t0 > ctx.timeout_ns;
+    if (__any_sync(0xffffffffu, flagged || late)) {
+      if (!flagged) {
+        *ctx.abort_flag = 1;
+        st_cluster_u32(ctx.peer_abort_addr, 1);
+        atomicCAS(ctx.status, 0u, code);
+      }
       return false;
     }
   }
+}
+
+// Bounded mbarrier wait (whole warp).  Returns false if the CTA was flagged or the wait ran out.
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                             uint32_t code) {
+  if (__all_sync(0xffffffffu, mbar_wait_spin(bar, parity, 8))) return true;
+  return wait_slow(bar, parity, ctx, code);
 }
 
 __device__ __forceinline__ void tile_coords(int tile, const TileParams& p, int& m_tile, int& n_tile) {
@@ -132,12 +188,24 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
   }
 }
 
-template <class Cfg>
+// kDebug compiles the per-role trace counters and the experiment switches in; the product
+// instantiation (kDebug == false) carries none of it in its loops.
+template <class Cfg, bool kDebug>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
   constexpr int G = Cfg::kCtaGroup;
   constexpr int kStages = Cfg::kStages;
+  unsigned long long* trace = nullptr;
+  unsigned int dbg = 0;
+  if constexpr (kDebug) {
+    trace = p.trace ? p.trace + (size_t)blockIdx.x * kTraceWords : nullptr;
+    dbg = p.debug_flags;
+    if (trace && threadIdx.x == 0) {
+      trace[kTraceEntry] = clock64();
+      trace[kTraceTimeEntryNs] = global_timer_ns();
+    }
+  }
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -148,13 +216,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t smem_b = base + kStages * Cfg::kABytes;
   const uint32_t smem_epi = smem_b + kStages * Cfg::kBBytes;
   uint8_t* bar_mem = smem + kStages * Cfg::kStageBytes + Cfg::kEpiBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(bar_mem);
-  // barrier indices
-  const uint32_t bar_base = smem_u32(bars);
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  // barrier block: full[kStages], empty[kStages], tfull[2], tempty[2], then two words
+  const uint32_t bar_base = smem_u32(bar_mem);
+  constexpr uint32_t kFullOff = 0, kEmptyOff = 8u * kStages, kTFullOff = 16u * kStages,
+                     kTEmptyOff = 16u * kStages + 16u;
   static_assert(8 * (2 * kStages + 4) + 8 <= Cfg::kBarrierBytes, "barrier block too small");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kStages + 4));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
@@ -177,12 +242,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     prefetch_tensormap(&tmap_b);
     prefetch_tensormap(&tmap_c);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);    // leader's producer arrives once and posts the byte count
-      mbar_init(empty_bar(s), 1);   // one tcgen05.commit per use
+      mbar_init(bar_base + kFullOff + 8u * s, 1);    // leader's producer arrives once and posts the byte count
+      mbar_init(bar_base + kEmptyOff + 8u * s, 1);   // one tcgen05.commit per use
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(tfull_bar(a), 1);          // one tcgen05.commit per tile
-      mbar_init(tempty_bar(a), 4 * G);     // every epilogue warp of the pair arrives once
+      mbar_init(bar_base + kTFullOff + 8u * a, 1);                     // one tcgen05.commit per use
+      mbar_init(bar_base + kTEmptyOff + 8u * a, Cfg::kEpiWarps * G);   // every epilogue warp of the pair arrives once
     }
     fence_mbar_init();
   }
@@ -198,148 +263,261 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if constexpr (kDebug)
+    if (trace && threadIdx.x == 0) trace[kTraceSetupDone] = clock64();
 
   const int num_tiles = p.m_tiles * p.n_tiles;
   const int first_tile = blockIdx.x / G;
   const int tile_step = gridDim.x / G;
+  const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
+  const int k_blocks = p.k_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp runs the loop, one elected lane issues.  The loop is flattened over
+    // (tile, k-block) and unrolled over the ring so that every barrier and shared-memory
+    // address is the ring base plus a constant.
+    if (!(kDebug && (dbg & kDebugSkipLoads))) {
+      const bool issuer = elect_one();
       const uint64_t pol = policy_evict_normal();
-      int stage = 0;
+      // Both CTAs of a pair complete their bytes on the LEADER's barrier: the leader's MMA
+      // thread is the only consumer of the ring.
+      const uint32_t full_leader = (G == 2) ? map_to_cta(bar_base + kFullOff, 0u) : bar_base + kFullOff;
       uint32_t phase = 0;
+      int remaining = my_tiles * k_blocks;
+      int kb = 0, tile = first_tile, row_a = 0, row_b = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-        int m_tile, n_tile;
-        tile_coords(tile, p, m_tile, n_tile);
-        const int row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
-        const int row_b = n_tile * Cfg::kBlockN + (int)cta_rank * Cfg::kBRows;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!wait_bounded(empty_bar(stage), phase ^ 1u, ctx, kStatusTimeoutProducer + stage)) {
+      long long stall = 0;
+      while (remaining > 0 && ok) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+          if (remaining == 0) break;
+          if (kb == 0) {
+            int m_tile, n_tile;
+            tile_coords(tile, p, m_tile, n_tile);
+            row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
+            row_b = n_tile * Cfg::kBlockN + (int)cta_rank * Cfg::kBRows;
+          }
+          long long t0 = 0;
+          if constexpr (kDebug) t0 = trace ? clock64() : 0;
+          if (!wait_bounded(bar_base + kEmptyOff + 8u * s, phase ^ 1u, ctx, kStatusTimeoutProducer + s)) {
             ok = false;
             break;
           }
-          // Both CTAs of a pair complete their bytes on the LEADER's barrier: the
-          // leader's MMA thread is the only consumer of the ring.
-          const uint32_t fb = (G == 2) ? map_to_cta(full_bar(stage), 0u) : full_bar(stage);
-          if (is_leader) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * G);
-          tma_load_2d<G>(smem_a + stage * Cfg::kABytes, &tmap_a, fb, kb * Cfg::kBlockK, row_a, pol);
-          tma_load_2d<G>(smem_b + stage * Cfg::kBBytes, &tmap_b, fb, kb * Cfg::kBlockK, row_b, pol);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+          if constexpr (kDebug)
+            if (trace) stall += clock64() - t0;
+          const int x = kb * Cfg::kBlockK;
+          if (issuer) {
+            if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
+            tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
+#pragma unroll
+            for (int h = 0; h < Cfg::kHalves; ++h)
+              tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, x,
+                             row_b + h * Cfg::kMmaN, pol);
           }
+          if (++kb == k_blocks) {
+            kb = 0;
+            tile += tile_step;
+          }
+          --remaining;
         }
+        phase ^= 1u;
       }
+      if constexpr (kDebug)
+        if (trace && issuer) {
+          trace[kTraceProdStall] = stall;
+          trace[kTraceProdEnd] = clock64();
+        }
     }
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0 && is_leader) {
-      constexpr uint32_t idesc =
-          make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kBlockN);
-      int stage = 0;
+    // The leader CTA's warp runs the loop, one elected lane issues.  Same flattening /
+    // unrolling as the producer: per ring slot the operand descriptors are the slot-0
+    // descriptors plus a constant.
+    if (is_leader) {
+      const bool issuer = elect_one();
+      constexpr uint32_t idesc = make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN);
+      const uint64_t da0 = make_smem_desc_sw128(smem_a);
+      const uint64_t db0 = make_smem_desc_sw128(smem_b);
+      const uint32_t bar_peer = (G == 2) ? map_to_cta(bar_base, 1u) : bar_base;
       uint32_t phase = 0;
+      int remaining = my_tiles * k_blocks;
+      int kb = 0, iter = 0;
       bool ok = true;
-      int iter = 0;
-      for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++iter) {
-        const int acc = iter & 1;
-        const uint32_t acc_phase = (iter >> 1) & 1u;
-        if (!wait_bounded(tempty_bar(acc), acc_phase ^ 1u, ctx, kStatusTimeoutMmaAcc + acc)) break;
-        tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + acc * Cfg::kBlockN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!wait_bounded(full_bar(stage), phase, ctx, kStatusTimeoutMma + stage)) {
+      long long stall_full = 0, stall_acc = 0;
+      const bool skip_mma = kDebug && (dbg & kDebugSkipMma);
+      while (remaining > 0 && ok) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+          if (remaining == 0) break;
+          long long tf = 0;
+          if constexpr (kDebug) tf = trace ? clock64() : 0;
+          if (!(kDebug && (dbg & kDebugSkipLoads)) &&
+              !wait_bounded(bar_base + kFullOff + 8u * s, phase, ctx, kStatusTimeoutMma + s)) {
             ok = false;
             break;
           }
+          if constexpr (kDebug)
+            if (trace) {
+              const long long now = clock64();
+              if (iter == 0 && kb == 0) {
+                if (issuer) trace[kTraceMmaFirst] = now;
+              } else {
+                stall_full += now - tf;
+              }
+            }
           tc_fence_after_sync();
-          const uint64_t da = make_smem_desc_sw128(smem_a + stage * Cfg::kABytes);
-          const uint64_t db = make_smem_desc_sw128(smem_b + stage * Cfg::kBBytes);
+          const bool last_kb = kb == k_blocks - 1;
 #pragma unroll
-          for (int k = 0; k < Cfg::kBlockK / Cfg::kUmmaK; ++k) {
-            // +32 bytes per 16-element K step inside the 128-byte swizzle row (>>4 encoded)
-            umma_f16<G>(tmem_d, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int h = 0; h < Cfg::kHalves; ++h) {
+            // accumulator slot of this half, and the parity of its hand-over barriers
+            const int slot = Cfg::kHalves == 1 ? (iter & 1) : h;
+            const uint32_t slot_phase = Cfg::kHalves == 1 ? ((iter >> 1) & 1u) : (iter & 1u);
+            if (kb == 0) {
+              long long ta = 0;
+              if constexpr (kDebug) ta = trace ? clock64() : 0;
+              if (!wait_bounded(bar_base + kTEmptyOff + 8u * slot, slot_phase ^ 1u, ctx,
+                                kStatusTimeoutMmaAcc + slot)) {
+                ok = false;
+                break;
+              }
+              if constexpr (kDebug)
+                if (trace) stall_acc += clock64() - ta;
+              tc_fence_after_sync();
+            }
+            const uint32_t tmem_d = tmem_base + slot * Cfg::kMmaN;
+            // descriptor address fields are in 16-byte units; +2 per 16-element K step (32 bytes
+            // inside the 128-byte swizzle row)
+            const uint64_t da = da0 + (uint64_t)((s * Cfg::kABytes) >> 4);
+            const uint64_t db = db0 + (uint64_t)((s * Cfg::kBBytes + h * Cfg::kBHalfBytes) >> 4);
+            if (issuer) {
+              if (!skip_mma) {
+                umma_f16<G>(tmem_d, da, db, idesc, kb != 0 ? 1u : 0u);    // first K step of a tile overwrites
+#pragma unroll
+                for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k)
+                  umma_f16<G>(tmem_d, da + 2u * k, db + 2u * k, idesc, 1u);
+              }
+              if (last_kb) {                                             // this half's accumulator is complete
+                if (skip_mma) {
+                  mbar_arrive_cluster_relaxed(bar_base + kTFullOff + 8u * slot);
+                  if constexpr (G == 2) mbar_arrive_cluster_relaxed(bar_peer + kTFullOff + 8u * slot);
+                } else {
+                  umma_commit<G>(bar_base + kTFullOff + 8u * slot);
+                  if constexpr (G == 2) umma_commit<G>(bar_peer + kTFullOff + 8u * slot);
+                }
+              }
+            }
           }
-          umma_commit<G>(empty_bar(stage));                       // slot reusable once MMAs retire
-          if constexpr (G == 2) umma_commit<G>(map_to_cta(empty_bar(stage), 1u));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+          if (!ok) break;
+          if (issuer) {
+            if (skip_mma) {
+              mbar_arrive_cluster_relaxed(bar_base + kEmptyOff + 8u * s);
+              if constexpr (G == 2) mbar_arrive_cluster_relaxed(bar_peer + kEmptyOff + 8u * s);
+            } else {
+              umma_commit<G>(bar_base + kEmptyOff + 8u * s);               // slot reusable once its MMAs retire
+              if constexpr (G == 2) umma_commit<G>(bar_peer + kEmptyOff + 8u * s);
+            }
           }
+          if (++kb == k_blocks) {
+            kb = 0;
+            ++iter;
+          }
+          --remaining;
         }
-        if (!ok) break;
-        umma_commit<G>(tfull_bar(acc));                           // accumulator ready
-        if constexpr (G == 2) umma_commit<G>(map_to_cta(tfull_bar(acc), 1u));
+        phase ^= 1u;
       }
+      if constexpr (kDebug)
+        if (trace && issuer) {
+          trace[kTraceMmaStallFull] = stall_full;
+          trace[kTraceMmaStallAcc] = stall_acc;
+          trace[kTraceMmaEnd] = clock64();
+          trace[kTraceTiles] = iter;
+        }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;                                  // TMEM lane quarter this warp may read
-    const uint32_t stage_buf = smem_epi + (uint32_t)(warp - 2) * 2u * Cfg::kEpiWarpBuf;
-    const uint32_t tempty_leader0 = (G == 2) ? map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
-    const uint32_t tempty_leader1 = (G == 2) ? map_to_cta(tempty_bar(1), 0u) : tempty_bar(1);
+    const int e = warp - 2;                                  // epilogue warp index
+    constexpr int kColGroups = Cfg::kEpiWarps / 4;           // warps sharing a lane quarter split the chunks
+    const int cg = e >> 2;
+    constexpr int kChunks = Cfg::kMmaN / Cfg::kEpiCols;      // 64-column chunks per accumulator slot
+    const uint32_t stage_buf = smem_epi + (uint32_t)e * Cfg::kEpiBufs * Cfg::kEpiWarpBuf;
+    const uint32_t tempty_leader = ((G == 2) ? map_to_cta(bar_base, 0u) : bar_base) + kTEmptyOff;
     int iter = 0;
     uint32_t buf = 0;
     bool ok = true;
+    long long stall = 0;
     for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++iter) {
       int m_tile, n_tile;
       tile_coords(tile, p, m_tile, n_tile);
-      const int acc = iter & 1;
-      const uint32_t acc_phase = (iter >> 1) & 1u;
       const int row0 = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + q * 32;
-      const int col0 = n_tile * Cfg::kBlockN;
-      if (!wait_bounded(tfull_bar(acc), acc_phase, ctx, kStatusTimeoutEpilogue + acc)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::kBlockN;
 #pragma unroll 1
-      for (int c = 0; c < Cfg::kBlockN / Cfg::kEpiCols; ++c) {
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32(taddr + c * Cfg::kEpiCols, v0);
-        tmem_ld_32x32(taddr + c * Cfg::kEpiCols + 32, v1);
-        tmem_ld_wait();
-        if (c == Cfg::kBlockN / Cfg::kEpiCols - 1) {
-          // All of this warp's reads of the accumulator are done: hand the buffer back.
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
+      for (int h = 0; ok && h < Cfg::kHalves; ++h) {
+        const int slot = Cfg::kHalves == 1 ? (iter & 1) : h;
+        const uint32_t slot_phase = Cfg::kHalves == 1 ? ((iter >> 1) & 1u) : (iter & 1u);
+        const int col0 = n_tile * Cfg::kBlockN + h * Cfg::kMmaN;
+        long long te = 0;
+        if constexpr (kDebug) te = trace ? clock64() : 0;
+        if (!wait_bounded(bar_base + kTFullOff + 8u * slot, slot_phase, ctx, kStatusTimeoutEpilogue + slot)) {
+          ok = false;
+          break;
         }
-        const bool live = (row0 < p.M) && (col0 + c * Cfg::kEpiCols < p.N);
-        if (live) {
-          // The staging buffer written two chunks ago must have been read by its store.
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-          const uint32_t dst = stage_buf + buf * Cfg::kEpiWarpBuf + lane * 128u;
+        if constexpr (kDebug)
+          if (trace) stall += clock64() - te;
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + slot * Cfg::kMmaN;
+#pragma unroll 1
+        for (int c = cg; c < kChunks; c += kColGroups) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(taddr + c * Cfg::kEpiCols, v0);
+          tmem_ld_32x32(taddr + c * Cfg::kEpiCols + 32, v1);
+          tmem_ld_wait();
+          if (c + kColGroups >= kChunks) {
+            // All of this warp's reads of the slot are done: hand it back to the MMA issuer.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * slot);
+          }
+          const bool live = (row0 < p.M) && (col0 + c * Cfg::kEpiCols < p.N) &&
+                            !(kDebug && (dbg & kDebugSkipStores));
+          if (live) {
+            // The staging buffer about to be rewritten must have been read by its store.
+            if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+            __syncwarp();
+            const uint32_t dst = stage_buf + buf * Cfg::kEpiWarpBuf + lane * 128u;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t* v = (j < 4) ? &v0[8 * j] : &v1[8 * (j - 4)];
-            const uint32_t w0 = pack2<Cfg::kIsBf16>(v[0], v[1]);
-            const uint32_t w1 = pack2<Cfg::kIsBf16>(v[2], v[3]);
-            const uint32_t w2 = pack2<Cfg::kIsBf16>(v[4], v[5]);
-            const uint32_t w3 = pack2<Cfg::kIsBf16>(v[6], v[7]);
-            // 16-byte chunk j of row `lane` lands at chunk j ^ (row % 8): the 128-byte swizzle
-            const uint32_t addr = dst + (((uint32_t)j ^ (lane & 7u)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
-                         "r"(w2), "r"(w3)
-                         : "memory");
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t* v = (j < 4) ? &v0[8 * j] : &v1[8 * (j - 4)];
+              const uint32_t w0 = pack2<Cfg::kIsBf16>(v[0], v[1]);
+              const uint32_t w1 = pack2<Cfg::kIsBf16>(v[2], v[3]);
+              const uint32_t w2 = pack2<Cfg::kIsBf16>(v[4], v[5]);
+              const uint32_t w3 = pack2<Cfg::kIsBf16>(v[6], v[7]);
+              // 16-byte chunk j of row `lane` lands at chunk j ^ (row % 8): the 128-byte swizzle
+              const uint32_t addr = dst + (((uint32_t)j ^ (lane & 7u)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
+                           "r"(w2), "r"(w3)
+                           : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, stage_buf + buf * Cfg::kEpiWarpBuf, col0 + c * Cfg::kEpiCols, row0);
+              tma_store_commit();
+            }
+            if constexpr (Cfg::kEpiBufs == 2) buf ^= 1u;
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmap_c, stage_buf + buf * Cfg::kEpiWarpBuf, col0 + c * Cfg::kEpiCols, row0);
-            tma_store_commit();
-          }
-          buf ^= 1u;
         }
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
+    if constexpr (kDebug)
+      if (trace && warp == 2 && lane == 0) {
+        trace[kTraceEpiStall] = stall;
+        trace[kTraceEpiEnd] = clock64();
+      }
   }
 
   // ------------------------------------------------------------------ tear-down
@@ -354,6 +532,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc<G>(tmem_base, Cfg::kTmemCols);
   }
+  if constexpr (kDebug)
+    if (trace && threadIdx.x == 0) {
+      trace[kTraceExit] = clock64();
+      trace[kTraceTimeExitNs] = global_timer_ns();
+    }
 }
 
 }  // namespace gemm_sm100

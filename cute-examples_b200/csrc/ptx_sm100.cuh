@@ -73,9 +73,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Arrive on a barrier that may live in another CTA of the cluster.
+// Arrive on a barrier that may live in another CTA of the cluster (default semantics:
+// release at CTA scope; a cluster-scope release costs a full memory fence per arrive).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// Arrive without release ordering (experiments that only count arrivals).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                : "memory");
 }
 
@@ -91,6 +97,44 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
+}
+
+// Up to `tries` try_wait attempts with the loop inside the asm block, so that the compiler's
+// control-flow graph around a wait stays warp-uniform (each try_wait suspends the thread for
+// a hardware-defined time while the phase is incomplete).  Returns whether the phase completed.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, uint32_t tries) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, %3;\n\t"
+      "WAIT_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra WAIT_DONE;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.ne.u32 p, n, 0;\n\t"
+      "@p bra WAIT_LOOP;\n\t"
+      "WAIT_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(tries)
+      : "memory");
+  return ok != 0;
+}
+
+// One lane of a converged warp (the same lane on every call).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // Generic-proxy writes to shared memory -> visible to the async proxy (TMA store).

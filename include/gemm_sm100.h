@@ -84,6 +84,16 @@ int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes);
  * device (negative on error). */
 int gemm_sm100_select_config(int M, int N, int K, int dtype);
 
+/* Profiling aid.  While a device buffer is registered, every launch whose grid fits
+ * (grid CTAs x 16 x 8 bytes <= bytes) writes one 16-word record per CTA: clock64 stamps of
+ * kernel entry, set-up done, first operand stage, last MMA issued, last load issued, epilogue
+ * done, exit; cycles each role spent waiting (MMA on operand stages [3] and on a free
+ * accumulator [4], producer on free ring slots [6], epilogue on accumulators [8]); tiles
+ * processed [11]; %globaltimer at entry [12] and exit [13].  NULL switches tracing off.
+ * The reference has no tracing in code; its profiler.py is a bare launch for Nsight
+ * (kernels/tests/profiler.py:1-12). */
+int gemm_sm100_set_trace_buffer(void* device_buffer, size_t bytes);
+
 /* Static, human-readable name of a return code. */
 const char* gemm_sm100_error_string(int code);
 

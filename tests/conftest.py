@@ -58,6 +58,8 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_describe_config.restype = I
     lib.gemm_sm100_select_config.argtypes = [I, I, I, I]
     lib.gemm_sm100_select_config.restype = I
+    lib.gemm_sm100_set_trace_buffer.argtypes = [P, Z]
+    lib.gemm_sm100_set_trace_buffer.restype = I
     lib.gemm_sm100_error_string.argtypes = [I]
     lib.gemm_sm100_error_string.restype = ctypes.c_char_p
     return lib

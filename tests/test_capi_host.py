@@ -39,6 +39,7 @@ def test_describe_and_options(capi):
         assert b"tile=" in buf.value and b"stages=" in buf.value
         n += 1
     assert n >= 4
+    assert b"epilogue_warps=" in buf.value
     assert capi.gemm_sm100_set_option(b"tile_config", n) == 9
     assert capi.gemm_sm100_set_option(b"tile_config", -1) == 0
     assert capi.gemm_sm100_set_option(b"timeout_ms", 0) == 9

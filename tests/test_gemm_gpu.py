@@ -20,7 +20,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 DT = {0: torch.bfloat16, 1: torch.float16}
-NUM_CONFIGS = 4
+NUM_CONFIGS = 7
 
 
 @pytest.fixture(scope="module")
@@ -58,7 +58,7 @@ def assert_close(C, C_ref, dtype, also_reference_check=False):
 
 # ------------------------------------------------------------ golden fixtures
 @pytest.mark.parametrize("name", ["small_bf16", "ragged_bf16", "small_fp16", "ternary_bf16", "ternary_fp16"])
-@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3])
+@pytest.mark.parametrize("config", [-1] + list(range(NUM_CONFIGS)))
 def test_golden_cases(capi, golden, name, config):
     M, N, K, seed, code, ternary = (int(x) for x in golden[f"{name}/meta"])
     dtype = DT[code]
@@ -137,7 +137,7 @@ EDGE_SHAPES = [
 
 
 @pytest.mark.parametrize("shape", EDGE_SHAPES)
-@pytest.mark.parametrize("config", [-1, 0, 2])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2])
 def test_edge_shapes(capi, shape, config):
     M, N, K = shape
     A, B = oracle.make_inputs(M, N, K, 40 + M % 7)
@@ -191,7 +191,7 @@ def test_binding_accepts_strided_c_view(gk):
 
 
 # ------------------------------------------- persistence / determinism / reuse
-@pytest.mark.parametrize("config,max_ctas", [(0, 2), (0, 6), (1, 4), (2, 1), (2, 3), (3, 5)])
+@pytest.mark.parametrize("config,max_ctas", [(0, 2), (0, 6), (1, 2), (1, 4), (2, 1), (2, 3), (3, 5), (4, 6), (5, 4), (6, 3)])
 def test_many_tiles_per_cta(capi, config, max_ctas):
     """Few CTAs, many tiles each: the accumulator buffers alternate and are reused, the smem
     ring wraps many times; a stale accumulator or a phase slip cannot hide."""
