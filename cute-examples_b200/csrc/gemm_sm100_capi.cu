@@ -154,9 +154,9 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // Cost model used to choose a tile configuration: time ~ waves x (per-CTA work of one tile) /
 // (relative rate of the configuration), where a wave is one tile on every resident CTA (pair).
 // Rates are measured on B200 at 8192^3 (power-capped steady state), relative to the 256 x 512
-// pair tile: the wider the tile, the fewer bytes reach shared memory per flop.
+// pair tile: the wider the tile, the fewer bytes cross L2 -> shared memory per flop.
 constexpr int kAutoConfigs = 4;                       // candidates of the automatic choice
-constexpr double kConfigRate[kAutoConfigs] = {0.87, 1.0, 0.72, 0.55};
+constexpr double kConfigRate[kAutoConfigs] = {0.96, 1.0, 0.72, 0.5};
 
 int choose_config(const Problem& p, int sm_count) {
   if (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) return static_cast<int>(g_opt_tile_config);
