@@ -58,6 +58,7 @@ long g_opt_timeout_ms = 2000;
 long g_opt_max_ctas = 0;
 long g_opt_debug_flags = 0;
 long g_opt_group_m = 0;
+long g_opt_split_k = -1;     // -1 automatic, 0 never, 1 whenever the configuration allows it
 unsigned long long* g_trace_ptr = nullptr;   // device buffer for per-CTA trace records, or null
 size_t g_trace_bytes = 0;
 
@@ -157,33 +158,77 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // pair tile: the wider the tile, the fewer bytes cross L2 -> shared memory per flop.
 constexpr int kAutoConfigs = 4;                       // candidates of the automatic choice
 constexpr double kConfigRate[kAutoConfigs] = {0.96, 1.0, 0.72, 0.5};
+constexpr int kSplitKConfig = 2;                      // the configuration that has a K-split variant
 
-int choose_config(const Problem& p, int sm_count) {
-  if (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) return static_cast<int>(g_opt_tile_config);
-  double best = 1e300;
-  int best_i = 0;
-  for (int i = 0; i < kAutoConfigs; ++i) {
+struct Plan {
+  int config = 0;
+  bool split_k = false;
+  int ctas = 0;              // grid size
+  size_t flag_bytes = 0;     // K-split: arrival counters (one per CTA), padded to 256 bytes
+  size_t partial_bytes = 0;  // K-split: one fp32 partial tile per CTA
+  int partial_rows = 128;    // K-split: rows kept per partial tile
+};
+
+inline int grid_cap(const ConfigInfo& c, int sm_count) {
+  long cap = sm_count - sm_count % c.cta_group;
+  if (g_opt_max_ctas > 0 && g_opt_max_ctas < cap) cap = g_opt_max_ctas - g_opt_max_ctas % c.cta_group;
+  if (cap < c.cta_group) cap = c.cta_group;
+  return static_cast<int>(cap);
+}
+
+// The K-split schedule gives every CTA the same number of K blocks; it pays when whole tiles
+// quantise badly over the SMs (few tiles, as in the memory-bound small-M shapes) and K is long.
+Plan make_plan(int M, int N, int K, int sm_count) {
+  Plan best;
+  double best_cost = 1e300;
+  const long k_blocks = ceil_div(K, 64);
+  const int first = (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) ? static_cast<int>(g_opt_tile_config) : 0;
+  const int last = (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) ? first + 1 : kAutoConfigs;
+  for (int i = first; i < last; ++i) {
     const ConfigInfo& c = kConfigs[i];
     const int block_n = c.mma_n * c.halves;
-    const long tiles = ceil_div(p.M, 128L * c.cta_group) * ceil_div(p.N, block_n);
-    const long slots = sm_count / c.cta_group;
+    const long tiles = ceil_div(M, 128L * c.cta_group) * ceil_div(N, block_n);
+    const int cap = grid_cap(c, sm_count);
+    const long slots = cap / c.cta_group;
     const long waves = ceil_div(tiles, slots);
-    const double cost = static_cast<double>(waves) * block_n / kConfigRate[i];
-    if (cost < best) {
-      best = cost;
-      best_i = i;
+    const double rate = i < kAutoConfigs ? kConfigRate[i] : 1.0;
+    Plan cand;
+    cand.config = i;
+    cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
+    double cost = static_cast<double>(waves) * block_n / rate;
+    const long units = tiles * k_blocks;
+    // Automatic choice: only when whole tiles would leave more than half of the SMs idle and
+    // every CTA still gets a long run of K blocks.  Forced (split_k = 1): whenever it is possible.
+    const bool can_split = i == kSplitKConfig && units >= 2;
+    const bool auto_split = g_opt_split_k < 0 && units >= slots * 8 && tiles * 2 <= slots;
+    if (can_split && (g_opt_split_k > 0 || auto_split)) {
+      const long ranges = units < slots ? units : slots;
+      cost = static_cast<double>(tiles) / ranges * block_n / rate * 1.04 + 8.0;
+      cand.split_k = true;
+      cand.ctas = static_cast<int>(ranges * c.cta_group);
+      cand.partial_rows = M < 128 ? static_cast<int>((M + 31) / 32 * 32) : 128;
+      cand.flag_bytes = (static_cast<size_t>(cand.ctas) * sizeof(unsigned int) + 255) / 256 * 256;
+      cand.partial_bytes = static_cast<size_t>(cand.ctas) * cand.partial_rows * block_n * sizeof(float);
+    }
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = cand;
     }
   }
-  return best_i;
+  return best;
 }
 
 template <int kCfgIndex, bool kIsBf16>
-int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
+int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceState& st, cudaStream_t stream,
+                  int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
   using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
   // The instrumented instantiation runs only while a trace buffer or an experiment flag is set.
   const bool debug = g_trace_ptr != nullptr || g_opt_debug_flags != 0;
   auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
+  if constexpr (kCfgIndex == kSplitKConfig) {
+    if (plan.split_k) kernel = gemm_tn_kernel<Cfg, false, true>;
+  }
   constexpr int dt = kIsBf16 ? 0 : 1;
   cudaError_t e;
 
@@ -194,6 +239,11 @@ int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* c
       if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
       e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
       if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      if constexpr (kCfgIndex == kSplitKConfig) {
+        e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::kSmemBytes);
+        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      }
       int max_ctas = st.sm_count;
       if (Cfg::kCtaGroup == 2) {
         cudaLaunchConfig_t qc = {};
@@ -231,6 +281,16 @@ int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* c
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
   tp.trace = nullptr;
   tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags);
+  tp.sk_flags = nullptr;
+  tp.sk_partials = nullptr;
+  tp.sk_rows = 128;
+  if (plan.split_k) {
+    tp.sk_flags = static_cast<unsigned int*>(workspace);
+    tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
+    tp.sk_rows = plan.partial_rows;
+    e = cudaMemsetAsync(tp.sk_flags, 0, plan.flag_bytes, stream);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  }
 
   CUtensorMap map_a, map_b, map_c;
   int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
@@ -240,11 +300,13 @@ int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* c
   rc = encode_2d(&map_c, p.C, p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
   if (rc) return rc;
 
-  long ctas = static_cast<long>(tp.m_tiles) * tp.n_tiles * Cfg::kCtaGroup;
-  long cap = st.max_ctas[kCfgIndex][dt];
-  if (g_opt_max_ctas > 0 && g_opt_max_ctas < cap) cap = g_opt_max_ctas - g_opt_max_ctas % Cfg::kCtaGroup;
-  if (cap < Cfg::kCtaGroup) cap = Cfg::kCtaGroup;
-  if (ctas > cap) ctas = cap;
+  long ctas = plan.ctas;
+  if (ctas > st.max_ctas[kCfgIndex][dt]) {
+    // Fewer co-resident CTAs than SMs (never seen on B200).  The K-split schedule needs the
+    // grid it was planned for, because the workspace is indexed by CTA.
+    if (plan.split_k) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
+    ctas = st.max_ctas[kCfgIndex][dt];
+  }
 
   if (g_trace_ptr && g_trace_bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
     tp.trace = g_trace_ptr;
@@ -267,17 +329,25 @@ int launch_config(const Problem& p, DeviceState& st, cudaStream_t stream, int* c
 }
 
 template <bool kIsBf16>
-int dispatch(int config, const Problem& p, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
-  switch (config) {
-    case 0: return launch_config<0, kIsBf16>(p, st, stream, cuda_error_out);
-    case 1: return launch_config<1, kIsBf16>(p, st, stream, cuda_error_out);
-    case 2: return launch_config<2, kIsBf16>(p, st, stream, cuda_error_out);
-    case 3: return launch_config<3, kIsBf16>(p, st, stream, cuda_error_out);
-    case 4: return launch_config<4, kIsBf16>(p, st, stream, cuda_error_out);
-    case 5: return launch_config<5, kIsBf16>(p, st, stream, cuda_error_out);
-    case 6: return launch_config<6, kIsBf16>(p, st, stream, cuda_error_out);
+int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
+  switch (plan.config) {
+    case 0: return launch_config<0, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 1: return launch_config<1, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 2: return launch_config<2, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 3: return launch_config<3, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 4: return launch_config<4, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 5: return launch_config<5, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 6: return launch_config<6, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
+}
+
+int current_sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) return g_dev[dev].sm_count;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  return n;
 }
 
 }  // namespace
@@ -287,8 +357,6 @@ extern "C" {
 int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
                   long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
                   int* cuda_error_out) {
-  (void)workspace;
-  (void)workspace_bytes;
   if (cuda_error_out) *cuda_error_out = 0;
   Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype};
   int rc = validate(p);
@@ -308,17 +376,21 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
     rc = get_encoder(cuda_error_out);
     if (rc != GEMM_SM100_OK) return rc;
   }
-  const int config = choose_config(p, st->sm_count);
-  if (dtype == GEMM_SM100_BF16) return dispatch<true>(config, p, *st, stream, cuda_error_out);
-  return dispatch<false>(config, p, *st, stream, cuda_error_out);
+  const Plan plan = make_plan(M, N, K, st->sm_count);
+  if (plan.split_k) {
+    if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
+        workspace_bytes < plan.flag_bytes + plan.partial_bytes)
+      return GEMM_SM100_ERR_WORKSPACE;
+  }
+  if (dtype == GEMM_SM100_BF16) return dispatch<true>(plan, p, workspace, *st, stream, cuda_error_out);
+  return dispatch<false>(plan, p, workspace, *st, stream, cuda_error_out);
 }
 
 size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype) {
-  (void)M;
-  (void)N;
-  (void)K;
   (void)dtype;
-  return 0;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const Plan plan = make_plan(M, N, K, current_sm_count());
+  return plan.split_k ? plan.flag_bytes + plan.partial_bytes : 0;
 }
 
 int gemm_sm100_num_sms(void) {
@@ -369,6 +441,11 @@ int gemm_sm100_set_option(const char* name, long value) {
     g_opt_debug_flags = value;
     return GEMM_SM100_OK;
   }
+  if (std::strcmp(name, "split_k") == 0) {
+    if (value < -1 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_split_k = value;
+    return GEMM_SM100_OK;
+  }
   if (std::strcmp(name, "group_m") == 0) {
     if (value < 0 || value > 4096) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_group_m = value;
@@ -400,11 +477,9 @@ int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes) {
 }
 
 int gemm_sm100_select_config(int M, int N, int K, int dtype) {
-  Problem p{nullptr, nullptr, nullptr, M, N, K, K, K, N, dtype};
+  (void)dtype;
   if (M <= 0 || N <= 0 || K <= 0) return -1;
-  int sms = gemm_sm100_num_sms();
-  if (sms <= 0) sms = 148;
-  return choose_config(p, sms);
+  return make_plan(M, N, K, current_sm_count()).config;
 }
 
 const char* gemm_sm100_error_string(int code) {

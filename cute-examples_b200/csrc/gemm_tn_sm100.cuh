@@ -42,6 +42,7 @@ enum : uint32_t {
   kStatusTimeoutMma = 0x200,
   kStatusTimeoutMmaAcc = 0x300,
   kStatusTimeoutEpilogue = 0x400,
+  kStatusTimeoutPartial = 0x500,    // a split tile's partial sums never arrived
 };
 
 struct TileParams {
@@ -54,6 +55,10 @@ struct TileParams {
   unsigned long long timeout_ns;   // bound of every device-side wait
   unsigned long long* trace;       // optional: kTraceWords counters per CTA (nullptr = off)
   unsigned int debug_flags;        // experiments only; 0 in normal use (see kDebug*)
+  // K-split schedule only: one arrival counter and one fp32 partial tile per CTA of the grid.
+  unsigned int* sk_flags;          // zeroed before the launch
+  float* sk_partials;              // grid x (sk_rows x kBlockN) floats
+  int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
 };
 
 // Experiment switches (results are garbage with any of them set).
@@ -120,6 +125,51 @@ struct GemmConfig {
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
+// A run of consecutive K blocks of one output tile.
+struct Segment {
+  int tile, kb0, kb1;
+};
+
+// What one CTA (pair) works on, as a sequence of segments.
+//  kSplitK == false: whole tiles `first, first + step, ...` (static persistent schedule).
+//  kSplitK == true : the flattened (tile, K block) space is cut into equal contiguous ranges,
+//    one per CTA (pair), so every SM streams the same number of K blocks whatever the tile
+//    count; a tile cut by a range boundary is summed by the owner of its first K block from
+//    fp32 partial tiles the other owners leave in global memory.
+template <bool kSplitK>
+struct WorkIter {
+  int tile, step, num_tiles, k_blocks;
+  long long u, u_end;
+
+  __device__ __forceinline__ static long long range_start(int cluster, int clusters, long long units) {
+    return (long long)cluster * units / clusters;
+  }
+  __device__ __forceinline__ WorkIter(int cluster, int clusters, int num_tiles_, int k_blocks_)
+      : tile(cluster), step(clusters), num_tiles(num_tiles_), k_blocks(k_blocks_) {
+    const long long units = (long long)num_tiles_ * k_blocks_;
+    u = range_start(cluster, clusters, units);
+    u_end = range_start(cluster + 1, clusters, units);
+  }
+  __device__ __forceinline__ bool next(Segment& s) {
+    if constexpr (!kSplitK) {
+      if (tile >= num_tiles) return false;
+      s.tile = tile;
+      s.kb0 = 0;
+      s.kb1 = k_blocks;
+      tile += step;
+      return true;
+    } else {
+      if (u >= u_end) return false;
+      s.tile = (int)(u / k_blocks);
+      s.kb0 = (int)(u - (long long)s.tile * k_blocks);
+      const long long left = u_end - u;
+      s.kb1 = (left < (long long)(k_blocks - s.kb0)) ? s.kb0 + (int)left : k_blocks;
+      u += s.kb1 - s.kb0;
+      return true;
+    }
+  }
+};
+
 struct WaitCtx {
   volatile uint32_t* abort_flag;   // this CTA's flag in shared memory
   uint32_t peer_abort_addr;        // shared::cluster address of the pair peer's flag (or own)
@@ -164,6 +214,34 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
   return wait_slow(bar, parity, ctx, code);
 }
 
+// Bounded wait (whole warp) until a global arrival counter reaches `want`.
+__device__ __noinline__ bool wait_counter(const unsigned int* counter, unsigned int want, const WaitCtx& ctx,
+                                          uint32_t code) {
+  const volatile unsigned int* c = counter;
+  uint64_t t0 = 0;
+#pragma unroll 1
+  for (unsigned int spin = 0;; ++spin) {
+    if (__all_sync(0xffffffffu, *c >= want)) {
+      __threadfence();   // acquire: the partial sums written before the arrivals are visible now
+      return true;
+    }
+    __nanosleep(100);
+    if ((spin & 255u) == 255u) {
+      if (t0 == 0) t0 = global_timer_ns();
+      const bool flagged = *ctx.abort_flag != 0;
+      const bool late = global_timer_ns() - t0 > ctx.timeout_ns;
+      if (__any_sync(0xffffffffu, flagged || late)) {
+        if (!flagged) {
+          *ctx.abort_flag = 1;
+          st_cluster_u32(ctx.peer_abort_addr, 1);
+          atomicCAS(ctx.status, 0u, code);
+        }
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void tile_coords(int tile, const TileParams& p, int& m_tile, int& n_tile) {
   // Groups of `group_m` tile-rows; inside a group M runs fastest, so the CTAs working at
   // the same time share few distinct A and B panels (L2 reuse).
@@ -190,7 +268,7 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
 
 // kDebug compiles the per-role trace counters and the experiment switches in; the product
 // instantiation (kDebug == false) carries none of it in its loops.
-template <class Cfg, bool kDebug>
+template <class Cfg, bool kDebug, bool kSplitK = false>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
@@ -267,9 +345,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (trace && threadIdx.x == 0) trace[kTraceSetupDone] = clock64();
 
   const int num_tiles = p.m_tiles * p.n_tiles;
-  const int first_tile = blockIdx.x / G;
-  const int tile_step = gridDim.x / G;
-  const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
+  const int cluster_id = blockIdx.x / G;
+  const int num_clusters = gridDim.x / G;
   const int k_blocks = p.k_blocks;
 
   if (warp == 0) {
@@ -284,19 +361,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // thread is the only consumer of the ring.
       const uint32_t full_leader = (G == 2) ? map_to_cta(bar_base + kFullOff, 0u) : bar_base + kFullOff;
       uint32_t phase = 0;
-      int remaining = my_tiles * k_blocks;
-      int kb = 0, tile = first_tile, row_a = 0, row_b = 0;
+      WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
+      Segment seg;
+      bool have = work.next(seg);
+      int kb = seg.kb0, row_a = 0, row_b = 0;
+      bool seg_start = true;
       bool ok = true;
       long long stall = 0;
-      while (remaining > 0 && ok) {
+      while (have && ok) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) {
-          if (remaining == 0) break;
-          if (kb == 0) {
+          if (!have) break;
+          if (seg_start) {
             int m_tile, n_tile;
-            tile_coords(tile, p, m_tile, n_tile);
+            tile_coords(seg.tile, p, m_tile, n_tile);
             row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
             row_b = n_tile * Cfg::kBlockN + (int)cta_rank * Cfg::kBRows;
+            seg_start = false;
           }
           long long t0 = 0;
           if constexpr (kDebug) t0 = trace ? clock64() : 0;
@@ -315,11 +396,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, x,
                              row_b + h * Cfg::kMmaN, pol);
           }
-          if (++kb == k_blocks) {
-            kb = 0;
-            tile += tile_step;
+          if (++kb == seg.kb1) {
+            have = work.next(seg);
+            kb = seg.kb0;
+            seg_start = true;
           }
-          --remaining;
         }
         phase ^= 1u;
       }
@@ -342,15 +423,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint64_t db0 = make_smem_desc_sw128(smem_b);
       const uint32_t bar_peer = (G == 2) ? map_to_cta(bar_base, 1u) : bar_base;
       uint32_t phase = 0;
-      int remaining = my_tiles * k_blocks;
-      int kb = 0, iter = 0;
+      WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
+      Segment seg;
+      bool have = work.next(seg);
+      int kb = seg.kb0, iter = 0;          // iter counts segments: it selects the accumulator slot
       bool ok = true;
       long long stall_full = 0, stall_acc = 0;
       const bool skip_mma = kDebug && (dbg & kDebugSkipMma);
-      while (remaining > 0 && ok) {
+      while (have && ok) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) {
-          if (remaining == 0) break;
+          if (!have) break;
           long long tf = 0;
           if constexpr (kDebug) tf = trace ? clock64() : 0;
           if (!(kDebug && (dbg & kDebugSkipLoads)) &&
@@ -361,20 +444,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if constexpr (kDebug)
             if (trace) {
               const long long now = clock64();
-              if (iter == 0 && kb == 0) {
+              if (iter == 0 && kb == seg.kb0) {
                 if (issuer) trace[kTraceMmaFirst] = now;
               } else {
                 stall_full += now - tf;
               }
             }
           tc_fence_after_sync();
-          const bool last_kb = kb == k_blocks - 1;
+          const bool first_kb = kb == seg.kb0;
+          const bool last_kb = kb == seg.kb1 - 1;
 #pragma unroll
           for (int h = 0; h < Cfg::kHalves; ++h) {
             // accumulator slot of this half, and the parity of its hand-over barriers
             const int slot = Cfg::kHalves == 1 ? (iter & 1) : h;
             const uint32_t slot_phase = Cfg::kHalves == 1 ? ((iter >> 1) & 1u) : (iter & 1u);
-            if (kb == 0) {
+            if (first_kb) {
               long long ta = 0;
               if constexpr (kDebug) ta = trace ? clock64() : 0;
               if (!wait_bounded(bar_base + kTEmptyOff + 8u * slot, slot_phase ^ 1u, ctx,
@@ -393,7 +477,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint64_t db = db0 + (uint64_t)((s * Cfg::kBBytes + h * Cfg::kBHalfBytes) >> 4);
             if (issuer) {
               if (!skip_mma) {
-                umma_f16<G>(tmem_d, da, db, idesc, kb != 0 ? 1u : 0u);    // first K step of a tile overwrites
+                umma_f16<G>(tmem_d, da, db, idesc, first_kb ? 0u : 1u);   // first K step of a segment overwrites
 #pragma unroll
                 for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k)
                   umma_f16<G>(tmem_d, da + 2u * k, db + 2u * k, idesc, 1u);
@@ -419,11 +503,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if constexpr (G == 2) umma_commit<G>(bar_peer + kEmptyOff + 8u * s);
             }
           }
-          if (++kb == k_blocks) {
-            kb = 0;
+          if (++kb == seg.kb1) {
+            have = work.next(seg);
+            kb = seg.kb0;
             ++iter;
           }
-          --remaining;
         }
         phase ^= 1u;
       }
@@ -449,10 +533,36 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t buf = 0;
     bool ok = true;
     long long stall = 0;
-    for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++iter) {
+    WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
+    Segment seg;
+    // K-split schedule: 16-byte pieces of a partial tile are laid out [piece][row][4 floats], so
+    // the 32 rows a warp owns are 512 contiguous bytes per piece.  Only rows below M exist.
+    const int sk_rows = kSplitK ? p.sk_rows : Cfg::kBlockM;
+    const size_t partial_floats = (size_t)sk_rows * Cfg::kBlockN;
+    const int my_row = q * 32 + (int)lane;                   // row of the CTA's 128 x kBlockN tile
+    for (; ok && work.next(seg); ++iter) {
       int m_tile, n_tile;
-      tile_coords(tile, p, m_tile, n_tile);
+      tile_coords(seg.tile, p, m_tile, n_tile);
       const int row0 = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + q * 32;
+      const bool row_live = row0 + (int)lane < p.M;          // rows past M hold zeros: never moved
+      const bool writes_partial = kSplitK && seg.kb0 != 0;
+      const bool reduces = kSplitK && seg.kb0 == 0 && seg.kb1 != k_blocks;
+      int writer_first = 0, writer_count = 0;
+      if constexpr (kSplitK) {
+        if (reduces) {
+          // The tile's later K blocks belong to the next CTA (pair)s in range order.
+          const long long units = (long long)num_tiles * k_blocks;
+          const long long tile_end = (long long)(seg.tile + 1) * k_blocks;
+          writer_first = cluster_id + 1;
+          while (writer_first + writer_count < num_clusters &&
+                 WorkIter<true>::range_start(writer_first + writer_count, num_clusters, units) < tile_end)
+            ++writer_count;
+          for (int w = 0; ok && w < writer_count; ++w)
+            ok = wait_counter(p.sk_flags + (size_t)(writer_first + w) * G + cta_rank, Cfg::kEpiWarps, ctx,
+                              kStatusTimeoutPartial);
+          if (!ok) break;
+        }
+      }
 #pragma unroll 1
       for (int h = 0; ok && h < Cfg::kHalves; ++h) {
         const int slot = Cfg::kHalves == 1 ? (iter & 1) : h;
@@ -479,6 +589,38 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * slot);
+          }
+          if constexpr (kSplitK) {
+            const int piece0 = (h * kChunks + c) * 16;       // first 16-byte piece of this chunk
+            if (writes_partial) {
+              if (row_live) {
+                float4* dst = reinterpret_cast<float4*>(p.sk_partials + (size_t)blockIdx.x * partial_floats) +
+                              (size_t)piece0 * sk_rows + my_row;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const uint32_t* v = (j < 8) ? &v0[4 * j] : &v1[4 * (j - 8)];
+                  dst[(size_t)j * sk_rows] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]),
+                                                               __uint_as_float(v[2]), __uint_as_float(v[3]));
+                }
+              }
+              continue;                                        // nothing goes to C from this segment
+            }
+            if (reduces && row_live) {
+              for (int w = 0; w < writer_count; ++w) {
+                const float4* src = reinterpret_cast<const float4*>(
+                                        p.sk_partials + ((size_t)(writer_first + w) * G + cta_rank) * partial_floats) +
+                                    (size_t)piece0 * sk_rows + my_row;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  uint32_t* v = (j < 8) ? &v0[4 * j] : &v1[4 * (j - 8)];
+                  const float4 t = __ldcg(src + (size_t)j * sk_rows);
+                  v[0] = __float_as_uint(__uint_as_float(v[0]) + t.x);
+                  v[1] = __float_as_uint(__uint_as_float(v[1]) + t.y);
+                  v[2] = __float_as_uint(__uint_as_float(v[2]) + t.z);
+                  v[3] = __float_as_uint(__uint_as_float(v[3]) + t.w);
+                }
+              }
+            }
           }
           const bool live = (row0 < p.M) && (col0 + c * Cfg::kEpiCols < p.N) &&
                             !(kDebug && (dbg & kDebugSkipStores));
@@ -508,6 +650,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             if constexpr (Cfg::kEpiBufs == 2) buf ^= 1u;
           }
+        }
+      }
+      if constexpr (kSplitK) {
+        if (ok && writes_partial) {
+          // Publish this warp's share of the partial tile: writes, fence, then one arrival.
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(p.sk_flags + blockIdx.x, 1u);
         }
       }
     }

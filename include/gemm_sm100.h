@@ -54,8 +54,10 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
                   long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
                   int* cuda_error_out);
 
-/* Bytes of scratch memory gemm_sm100_tn needs for this problem (0 for most shapes; non-zero
- * when the memory-bound small-M path splits K).  No reference counterpart: the reference
+/* Bytes of scratch memory gemm_sm100_tn needs for this problem on the current device: 0 for
+ * most shapes; non-zero when the K-split schedule is chosen (few tiles and long K, e.g. the
+ * memory-bound small-M shapes), which keeps one arrival counter and one fp32 partial tile per
+ * CTA there.  The contents need no initialisation.  No reference counterpart: the reference
  * kernel needs no workspace (gemm_test.cu:70-85). */
 size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype);
 
@@ -72,7 +74,10 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
 
 /* Tuning / test knobs, process-wide.  Names: "tile_config" (-1 = choose automatically,
  * otherwise an index reported by gemm_sm100_describe_config), "timeout_ms" (bound of each
- * device-side wait, default 2000), "max_ctas" (0 = all SMs; caps the persistent grid).
+ * device-side wait, default 2000), "max_ctas" (0 = all SMs; caps the persistent grid),
+ * "split_k" (-1 = automatic, 0 = never, 1 = whenever the chosen configuration has a K-split
+ * variant), "group_m" (0 = default; tile rows per rasterisation group).  Set them before
+ * asking gemm_sm100_workspace_bytes, which depends on them.
  * The reference's equivalents are compile-time constants (gemm.cuh:420-451). */
 int gemm_sm100_set_option(const char* name, long value);
 

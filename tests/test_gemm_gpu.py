@@ -37,6 +37,7 @@ def _reset_options(capi):
     yield
     capi.gemm_sm100_set_option(b"tile_config", -1)
     capi.gemm_sm100_set_option(b"max_ctas", 0)
+    capi.gemm_sm100_set_option(b"split_k", -1)
 
 
 def run_capi(capi, A, B, prefill=float("nan")):
@@ -204,6 +205,55 @@ def test_many_tiles_per_cta(capi, config, max_ctas):
     At, Bt = oracle.make_ternary_inputs(M, N, 256, 61)
     Ct = run_capi(capi, At, Bt)
     assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+# ------------------------------------------------------------- K-split schedule
+SPLIT_SHAPES = [
+    # M, N, K, max_ctas: tiles of 128 x 256 cut at range boundaries that fall inside tiles
+    (128, 2048, 4096, 0), (16, 28672 // 4, 2048, 0), (64, 1024, 8192, 0), (128, 512, 1024, 5),
+    (300, 1000, 1536, 7), (256, 256, 64 * 40, 3), (100, 264, 4104, 0), (128, 256, 64 * 37, 148),
+]
+
+
+@pytest.mark.parametrize("shape", SPLIT_SHAPES)
+def test_split_k_matches_oracle(capi, shape):
+    M, N, K, max_ctas = shape
+    A, B = oracle.make_inputs(M, N, K, 80 + M % 5)
+    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"split_k", 1)
+    capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
+    assert capi.gemm_sm100_workspace_bytes(M, N, K, 0) > 0
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    # same bits on a second run (partial sums are added in a fixed order)
+    C2 = run_capi(capi, A, B)
+    assert torch.equal(C.view(torch.int16), C2.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_split_k_exact_on_integers(capi, dtype):
+    """Integer-valued sums are exact in fp32 however K is cut, so the K-split result must equal
+    the unsplit one bit for bit."""
+    M, N, K = 128, 1536, 256
+    A, B = oracle.make_ternary_inputs(M, N, K, 81, dtype)
+    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"split_k", 1)
+    capi.gemm_sm100_set_option(b"max_ctas", 11)
+    C = run_capi(capi, A, B)
+    assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
+
+
+def test_split_k_rejects_missing_workspace(capi):
+    M, N, K = 128, 2048, 4096
+    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"split_k", 1)
+    A = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    err = ctypes.c_int(0)
+    rc = capi.gemm_sm100_tn(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0, None, 0, None,
+                            ctypes.byref(err))
+    assert rc == 7          # GEMM_SM100_ERR_WORKSPACE, nothing launched
 
 
 def test_deterministic(capi):
