@@ -26,6 +26,12 @@ using namespace gemm_sm100;
 // One status word per device (a __device__ variable exists once per device).
 __device__ unsigned int g_status_word;
 
+// Scratch of gemm_sm100_tn_static_scratch: arrival counters (first kStaticFlagBytes) followed by
+// fp32 partial tiles.  Every device that loads this library holds one copy until exit.
+constexpr size_t kStaticFlagBytes = 1024;
+constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 constexpr int kMaxDevices = 64;
 constexpr int kNumConfigs = 7;
 
@@ -47,6 +53,7 @@ struct DeviceState {
   int sm_count = 0;
   int cc_major = 0;
   unsigned int* status_ptr = nullptr;
+  void* static_scratch = nullptr;      // device address of g_static_scratch on this device
   int max_ctas[kNumConfigs][2] = {};   // persistent grid limit per config and dtype
   bool attr_set[kNumConfigs][2] = {};
 };
@@ -386,6 +393,63 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
   return dispatch<false>(plan, p, workspace, *st, stream, cuda_error_out);
 }
 
+int gemm_sm100_tn_static_scratch(const void* A, const void* B, void* C, int M, int N, int K, long lda,
+                                 long ldb, long ldc, int dtype, void* cuda_stream, int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype};
+  int rc = validate(p);
+  if (rc != GEMM_SM100_OK) return rc;
+  if (M == 0 || N == 0) return GEMM_SM100_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (K == 0) {
+    cudaError_t e = cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 2, 0, static_cast<size_t>(N) * 2,
+                                      static_cast<size_t>(M), stream);
+    return e == cudaSuccess ? GEMM_SM100_OK : set_cuda_error(cuda_error_out, e);
+  }
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    rc = get_encoder(cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    if (st->static_scratch == nullptr) {
+      // Once per device, with that device current.  In host code the array's name is only a
+      // handle for this lookup; the kernel must be given the address the runtime returns.
+      void* ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      st->static_scratch = ptr;
+    }
+  }
+  // The 128 x 256 single-CTA configuration with the K-split schedule whenever the problem has
+  // at least two K blocks of work to divide (otherwise one whole tile, which needs no scratch).
+  const ConfigInfo& c = kConfigs[kSplitKConfig];
+  const int block_n = c.mma_n * c.halves;
+  const long tiles = ceil_div(M, 128L) * ceil_div(N, block_n);
+  const long units = tiles * ceil_div(K, 64);
+  const long slots = grid_cap(c, st->sm_count);
+  Plan plan;
+  plan.config = kSplitKConfig;
+  if (units >= 2) {
+    const long ranges = units < slots ? units : slots;
+    plan.split_k = true;
+    plan.ctas = static_cast<int>(ranges);
+    plan.partial_rows = M < 128 ? static_cast<int>((M + 31) / 32 * 32) : 128;
+    plan.flag_bytes = kStaticFlagBytes;
+    plan.partial_bytes = static_cast<size_t>(plan.ctas) * plan.partial_rows * block_n * sizeof(float);
+    if (static_cast<size_t>(plan.ctas) * sizeof(unsigned int) > kStaticFlagBytes ||
+        plan.flag_bytes + plan.partial_bytes > kStaticScratchBytes)
+      return GEMM_SM100_ERR_STATIC_SCRATCH;
+  } else {
+    plan.ctas = static_cast<int>(tiles < slots ? tiles : slots);
+  }
+  if (dtype == GEMM_SM100_BF16) return dispatch<true>(plan, p, st->static_scratch, *st, stream, cuda_error_out);
+  return dispatch<false>(plan, p, st->static_scratch, *st, stream, cuda_error_out);
+}
+
+size_t gemm_sm100_static_scratch_capacity(void) { return kStaticScratchBytes; }
+
 size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype) {
   (void)dtype;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -494,6 +558,9 @@ const char* gemm_sm100_error_string(int code) {
     case GEMM_SM100_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
     case GEMM_SM100_ERR_UNSUPPORTED_DEVICE: return "device is not sm_100";
     case GEMM_SM100_ERR_BAD_OPTION: return "unknown option or value out of range";
+    case GEMM_SM100_ERR_STATIC_SCRATCH:
+      return "problem needs more scratch than the built-in array of gemm_sm100_tn_static_scratch holds "
+             "(M above 32 on a full-size GPU); use gemm_sm100_tn with a caller workspace";
     default: return "unknown error code";
   }
 }

@@ -32,6 +32,7 @@ extern "C" {
 #define GEMM_SM100_ERR_WORKSPACE 7        /* workspace missing, misaligned or too small */
 #define GEMM_SM100_ERR_UNSUPPORTED_DEVICE 8 /* current device is not compute capability 10.x */
 #define GEMM_SM100_ERR_BAD_OPTION 9
+#define GEMM_SM100_ERR_STATIC_SCRATCH 10  /* problem too large for gemm_sm100_tn_static_scratch */
 
 /* Element types of A, B and C. */
 #define GEMM_SM100_BF16 0
@@ -53,6 +54,36 @@ extern "C" {
 int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
                   long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
                   int* cuda_error_out);
+
+/* Same product C = A * B^T as gemm_sm100_tn, for hosts that have no way to hand this library
+ * scratch memory and must not see it allocate any: an operator plugged into a serving stack
+ * that owns the whole device through its own pool and passes only input and output buffers, a
+ * binding whose call signature has no workspace slot, or a latency-critical loop where a
+ * cudaMalloc (which synchronises the device) is not acceptable.  It has no counterpart in the
+ * reference, whose kernel needs no scratch at all.
+ *
+ * It always runs the 128 x 256-tile kernel with the K-split schedule (every CTA gets an equal
+ * run of K blocks; tiles cut by a range boundary are summed from fp32 partial tiles), and keeps
+ * the arrival counters and partial tiles in an array built into the library
+ * (gemm_sm100_static_scratch_capacity() bytes, 5 MiB + 1 KiB, resident on every GPU that loads
+ * the library until the process exits).  One partial tile of round_up(min(M,128), 32) x 256
+ * floats per CTA must fit: on a 148-SM GPU that means M <= 32 (the few-rows, long-K shapes the
+ * schedule is meant for); anything larger is refused with GEMM_SM100_ERR_STATIC_SCRATCH and
+ * nothing is launched.  Arguments, requirements and the other return codes are those of
+ * gemm_sm100_tn.
+ *
+ * The call allocates nothing (no cudaMalloc, no cudaFree, no allocating library routine); it
+ * zeroes the counters on `cuda_stream` before the kernel.  The first call on each device looks
+ * up the array's device address (cudaGetSymbolAddress, with that device current): make that
+ * first call before starting any stream capture.  All calls on a device share the one array,
+ * which keeps whatever the previous call left in it: two calls whose GPU work can overlap
+ * (different streams without an ordering between them) race on it and give wrong results;
+ * calls on one stream, or otherwise ordered, are safe. */
+int gemm_sm100_tn_static_scratch(const void* A, const void* B, void* C, int M, int N, int K, long lda,
+                                 long ldb, long ldc, int dtype, void* cuda_stream, int* cuda_error_out);
+
+/* Size in bytes of the array gemm_sm100_tn_static_scratch works in. */
+size_t gemm_sm100_static_scratch_capacity(void);
 
 /* Bytes of scratch memory gemm_sm100_tn needs for this problem on the current device: 0 for
  * most shapes; non-zero when the K-split schedule is chosen (few tiles and long K, e.g. the

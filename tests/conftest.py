@@ -46,6 +46,10 @@ def load_capi() -> ctypes.CDLL:
     I, L, P, Z = ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_size_t
     lib.gemm_sm100_tn.argtypes = [P, P, P, I, I, I, L, L, L, I, P, Z, P, ctypes.POINTER(I)]
     lib.gemm_sm100_tn.restype = I
+    lib.gemm_sm100_tn_static_scratch.argtypes = [P, P, P, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]
+    lib.gemm_sm100_tn_static_scratch.restype = I
+    lib.gemm_sm100_static_scratch_capacity.argtypes = []
+    lib.gemm_sm100_static_scratch_capacity.restype = Z
     lib.gemm_sm100_workspace_bytes.argtypes = [I, I, I, I]
     lib.gemm_sm100_workspace_bytes.restype = Z
     lib.gemm_sm100_num_sms.argtypes = []
