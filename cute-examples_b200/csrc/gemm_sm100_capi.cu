@@ -56,6 +56,8 @@ struct DeviceState {
   void* static_scratch = nullptr;      // device address of g_static_scratch on this device
   int max_ctas[kNumConfigs][2] = {};   // persistent grid limit per config and dtype
   bool attr_set[kNumConfigs][2] = {};
+  bool fanout_attr_set[2][2] = {};
+  bool pf_attr_set[kNumConfigs][2] = {};
 };
 
 std::mutex g_mutex;
@@ -65,6 +67,7 @@ long g_opt_timeout_ms = 2000;
 long g_opt_max_ctas = 0;
 long g_opt_debug_flags = 0;
 long g_opt_group_m = 0;
+long g_opt_l2_prefetch = 0;   // K blocks of L2 prefetch distance (0 = off)
 long g_opt_split_k = -1;     // -1 automatic, 0 never, 1 whenever the configuration allows it
 unsigned long long* g_trace_ptr = nullptr;   // device buffer for per-CTA trace records, or null
 size_t g_trace_bytes = 0;
@@ -96,15 +99,16 @@ int get_encoder(int* cuda_error_out) {
 // Tensor map of a row-major 2-D array of 16-bit elements: `rows` x `cols`, pitch `ld`
 // elements, box `box_rows` x 64 columns, 128-byte swizzle (64 x 2 B = one swizzle row).
 int encode_2d(CUtensorMap* map, const void* base, int dtype, long rows, long cols, long ld,
-              int box_rows, int* cuda_error_out) {
+              int box_rows, int* cuda_error_out, int box_cols = 64) {
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
-  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem_strides[2] = {1u, 1u};
   const CUtensorMapDataType dt =
       dtype == GEMM_SM100_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_cuda_error(cuda_error_out, cudaErrorInvalidValue);
   return GEMM_SM100_OK;
@@ -330,7 +334,103 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   attrs[0].val.clusterDim.z = 1;
   cfg.attrs = attrs;
   cfg.numAttrs = 1;
+  tp.pf_blocks = 0;
+  if (g_opt_l2_prefetch > 0 && !debug) {
+    PrefetchMaps pf;
+    rc = encode_2d(&pf.maps[0], p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out, 256);
+    if (rc) return rc;
+    rc = encode_2d(&pf.maps[1], p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out, 256);
+    if (rc) return rc;
+    tp.pf_blocks = static_cast<int>(g_opt_l2_prefetch);
+    auto pf_kernel = gemm_tn_prefetch_kernel<Cfg, false>;
+    if constexpr (kCfgIndex == kSplitKConfig) {
+      if (plan.split_k) pf_kernel = gemm_tn_prefetch_kernel<Cfg, true>;
+    }
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      if (!st.pf_attr_set[kCfgIndex][dt]) {
+        e = cudaFuncSetAttribute(gemm_tn_prefetch_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::kSmemBytes);
+        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+        if constexpr (kCfgIndex == kSplitKConfig) {
+          e = cudaFuncSetAttribute(gemm_tn_prefetch_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   Cfg::kSmemBytes);
+          if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+        }
+        st.pf_attr_set[kCfgIndex][dt] = true;
+      }
+    }
+    e = cudaLaunchKernelEx(&cfg, pf_kernel, map_a, map_b, map_c, pf, tp);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    return GEMM_SM100_OK;
+  }
   e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  return GEMM_SM100_OK;
+}
+
+// Launch of the store-to-every-output variant (pair-tile configurations 0 and 1 only).
+template <int kCfgIndex, bool kIsBf16>
+int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, DeviceState& st, cudaStream_t stream,
+                  int* cuda_error_out) {
+  constexpr ConfigInfo ci = kConfigs[kCfgIndex];
+  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  auto kernel = gemm_tn_fanout_kernel<Cfg>;
+  constexpr int dt = kIsBf16 ? 0 : 1;
+  cudaError_t e;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!st.fanout_attr_set[kCfgIndex][dt]) {
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      st.fanout_attr_set[kCfgIndex][dt] = true;
+    }
+  }
+  TileParams tp;
+  tp.M = p.M;
+  tp.N = p.N;
+  tp.K = p.K;
+  tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
+  tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
+  tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
+  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : 8;
+  tp.status = st.status_ptr;
+  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
+  tp.trace = nullptr;
+  tp.debug_flags = 0;
+  tp.sk_flags = nullptr;
+  tp.sk_partials = nullptr;
+  tp.sk_rows = 128;
+  tp.pf_blocks = 0;
+
+  CUtensorMap map_a, map_b;
+  OutputMaps out;
+  std::memset(&out, 0, sizeof(out));
+  int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  if (rc) return rc;
+  rc = encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
+  if (rc) return rc;
+  for (int d = 0; d < num_outputs; ++d) {
+    rc = encode_2d(&out.maps[d], outputs[d], p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
+    if (rc) return rc;
+  }
+  long ctas = static_cast<long>(tp.m_tiles) * tp.n_tiles * Cfg::kCtaGroup;
+  const long cap = grid_cap(ci, st.sm_count);
+  if (ctas > cap) ctas = cap;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = Cfg::kCtaGroup;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, out, num_outputs, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -448,6 +548,54 @@ int gemm_sm100_tn_static_scratch(const void* A, const void* B, void* C, int M, i
   return dispatch<false>(plan, p, st->static_scratch, *st, stream, cuda_error_out);
 }
 
+int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int num_outputs, int M, int N,
+                         int K, long lda, long ldb, long ldc, int dtype, void* cuda_stream, int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  if (outputs == nullptr) return GEMM_SM100_ERR_NULL_POINTER;
+  if (num_outputs < 1 || num_outputs > kMaxOutputs) return GEMM_SM100_ERR_BAD_SHAPE;
+  for (int d = 0; d < num_outputs; ++d) {
+    Problem pd{A, B, outputs[d], M, N, K, lda, ldb, ldc, dtype};
+    const int rc = validate(pd);
+    if (rc != GEMM_SM100_OK) return rc;
+  }
+  if (M == 0 || N == 0) return GEMM_SM100_OK;
+  if (K == 0) return GEMM_SM100_ERR_BAD_SHAPE;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    rc = get_encoder(cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+  }
+  Problem p{A, B, outputs[0], M, N, K, lda, ldb, ldc, dtype};
+  // Pair-tile configurations only; the same wave model as the plain GEMM picks between them.
+  const long slots = st->sm_count / 2;
+  const double cost0 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 256L), slots)) * 256 / kConfigRate[0];
+  const double cost1 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 512L), slots)) * 512 / kConfigRate[1];
+  const bool wide = g_opt_tile_config == 1 || (g_opt_tile_config != 0 && cost1 <= cost0);
+  if (dtype == GEMM_SM100_BF16)
+    return wide ? launch_fanout<1, true>(p, outputs, num_outputs, *st, stream, cuda_error_out)
+                : launch_fanout<0, true>(p, outputs, num_outputs, *st, stream, cuda_error_out);
+  return wide ? launch_fanout<1, false>(p, outputs, num_outputs, *st, stream, cuda_error_out)
+              : launch_fanout<0, false>(p, outputs, num_outputs, *st, stream, cuda_error_out);
+}
+
+int gemm_sm100_selftest_wait_timeout(void* cuda_stream, int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    const int rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+  }
+  wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      st->status_ptr, static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? GEMM_SM100_OK : set_cuda_error(cuda_error_out, e);
+}
+
 size_t gemm_sm100_static_scratch_capacity(void) { return kStaticScratchBytes; }
 
 size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype) {
@@ -503,6 +651,11 @@ int gemm_sm100_set_option(const char* name, long value) {
   if (std::strcmp(name, "debug_flags") == 0) {
     if (value < 0 || value > 7) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_debug_flags = value;
+    return GEMM_SM100_OK;
+  }
+  if (std::strcmp(name, "l2_prefetch") == 0) {
+    if (value < 0 || value > 256) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_l2_prefetch = value;
     return GEMM_SM100_OK;
   }
   if (std::strcmp(name, "split_k") == 0) {

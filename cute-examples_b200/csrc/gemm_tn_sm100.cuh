@@ -59,6 +59,9 @@ struct TileParams {
   unsigned int* sk_flags;          // zeroed before the launch
   float* sk_partials;              // grid x (sk_rows x kBlockN) floats
   int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
+  // Optional L2 prefetch of the operands in runs of 4 K blocks (512 contiguous bytes per row), so
+  // that DRAM sees longer bursts than the 128-byte rows of the shared-memory tiles.
+  int pf_blocks;                   // how many K blocks ahead of the loads the prefetch runs (0 = off)
 };
 
 // Experiment switches (results are garbage with any of them set).
@@ -268,10 +271,15 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
 
 // kDebug compiles the per-role trace counters and the experiment switches in; the product
 // instantiation (kDebug == false) carries none of it in its loops.
-template <class Cfg, bool kDebug, bool kSplitK = false>
-__global__ void __launch_bounds__(Cfg::kThreads, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
+//
+// `tmap_c` points at `num_c` tensor maps of the output: the finished tile is stored through
+// every one of them (one for the plain GEMM; the column-sharded multi-GPU path passes one map
+// per GPU, each describing this rank's column slab inside that GPU's C, so the all-gather of C
+// happens in the epilogue as TMA stores over NVLink).
+template <class Cfg, bool kDebug, bool kSplitK>
+__device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                             const CUtensorMap* tmap_c, const int num_c, const TileParams& p,
+                                             const CUtensorMap* pf_maps = nullptr) {
   constexpr int G = Cfg::kCtaGroup;
   constexpr int kStages = Cfg::kStages;
   unsigned long long* trace = nullptr;
@@ -318,7 +326,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     *abort_flag = 0;
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
-    prefetch_tensormap(&tmap_c);
+    for (int d = 0; d < num_c; ++d) prefetch_tensormap(tmap_c + d);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_base + kFullOff + 8u * s, 1);    // leader's producer arrives once and posts the byte count
       mbar_init(bar_base + kEmptyOff + 8u * s, 1);   // one tcgen05.commit per use
@@ -388,6 +396,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if constexpr (kDebug)
             if (trace) stall += clock64() - t0;
           const int x = kb * Cfg::kBlockK;
+          if (pf_maps != nullptr && p.pf_blocks > 0 && issuer) {
+            // Every 4th K block (and at the start of a segment) pull the next run of 4 K blocks
+            // of this tile's A and B rows into L2: pf_maps[0] / [1] have 256-element-wide boxes.
+            const bool at_start = kb == seg.kb0;
+            if (at_start || (kb & 3) == 0) {
+              const int first = at_start ? (kb & ~3) : ((kb & ~3) + p.pf_blocks);
+              const int last = (kb & ~3) + p.pf_blocks;
+              for (int b = first; b <= last; b += 4) {
+                if (b < seg.kb1) {
+                  tma_prefetch_l2_2d(pf_maps, b * Cfg::kBlockK, row_a);
+#pragma unroll
+                  for (int h = 0; h < Cfg::kHalves; ++h)
+                    tma_prefetch_l2_2d(pf_maps + 1, b * Cfg::kBlockK, row_b + h * Cfg::kMmaN);
+                }
+              }
+            }
+          }
           if (issuer) {
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
             tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
@@ -645,7 +670,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&tmap_c, stage_buf + buf * Cfg::kEpiWarpBuf, col0 + c * Cfg::kEpiCols, row0);
+              for (int d = 0; d < num_c; ++d)
+                tma_store_2d(tmap_c + d, stage_buf + buf * Cfg::kEpiWarpBuf, col0 + c * Cfg::kEpiCols, row0);
               tma_store_commit();
             }
             if constexpr (Cfg::kEpiBufs == 2) buf ^= 1u;
@@ -687,6 +713,59 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       trace[kTraceExit] = clock64();
       trace[kTraceTimeExitNs] = global_timer_ns();
     }
+}
+
+template <class Cfg, bool kDebug, bool kSplitK = false>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
+  gemm_tn_body<Cfg, kDebug, kSplitK>(tmap_a, tmap_b, &tmap_c, 1, p);
+}
+
+// Operand maps with 256-element-wide boxes, used only for L2 prefetch ([0] = A, [1] = B).
+struct PrefetchMaps {
+  CUtensorMap maps[2];
+};
+
+template <class Cfg, bool kSplitK = false>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+gemm_tn_prefetch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PrefetchMaps pf,
+                        const TileParams p) {
+  gemm_tn_body<Cfg, false, kSplitK>(tmap_a, tmap_b, &tmap_c, 1, p, pf.maps);
+}
+
+// Self-test of the bounded wait: one warp waits on a barrier that nothing ever arrives on.  The
+// wait must give up after the time limit, record kStatusSelfTest and let the kernel return.
+constexpr uint32_t kStatusSelfTest = 0x7e57;
+__global__ void __launch_bounds__(32, 1) wait_timeout_selftest_kernel(unsigned int* status, unsigned long long timeout_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  WaitCtx ctx;
+  ctx.abort_flag = &abort_flag;
+  ctx.peer_abort_addr = smem_u32(&abort_flag);
+  ctx.status = status;
+  ctx.timeout_ns = timeout_ns;
+  (void)wait_bounded(smem_u32(&bar), 0u, ctx, kStatusSelfTest);
+}
+
+// Output tensor maps of the store-to-every-GPU variant.
+constexpr int kMaxOutputs = 8;
+struct OutputMaps {
+  CUtensorMap maps[kMaxOutputs];
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+gemm_tn_fanout_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ OutputMaps outputs, const int num_outputs, const TileParams p) {
+  gemm_tn_body<Cfg, false, false>(tmap_a, tmap_b, outputs.maps, num_outputs, p);
 }
 
 }  // namespace gemm_sm100

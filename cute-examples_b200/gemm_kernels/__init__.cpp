@@ -9,6 +9,7 @@
 #include <torch/extension.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/gemm_sm100.h"
 
@@ -38,8 +39,11 @@ torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "All tensors must be CUDA tensors");
   TORCH_CHECK(A.device() == B.device() && A.device() == C.device(),
               "All tensors must be on the same device");
-  TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "All tensors must be contiguous");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "Both tensors must be 2D (matrix) tensors");
+  // The reference insists on contiguous operands (gemm_test.cu:18-19); rows with a larger pitch
+  // are accepted here as long as K stays contiguous.
+  TORCH_CHECK((A.numel() == 0 || A.stride(1) == 1) && (B.numel() == 0 || B.stride(1) == 1),
+              "All tensors must be contiguous along K");
   TORCH_CHECK(A.size(1) == B.size(1), "Inner dimensions of A and B must match (A: ", A.size(1),
               ", B: ", B.size(1), ")");
   const int dtype = dtype_code(A);
@@ -66,16 +70,48 @@ torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::
   }
   cudaStream_t stream = c10::cuda::getCurrentCUDAStream(A.device().index()).stream();
   const long ldc = M > 1 ? static_cast<long>(C.stride(0)) : static_cast<long>(N);
+  const long lda = M > 1 ? static_cast<long>(A.stride(0)) : static_cast<long>(K);
+  const long ldb = N > 1 ? static_cast<long>(B.stride(0)) : static_cast<long>(K);
   int cuda_error = 0;
   int rc;
   {
     pybind11::gil_scoped_release release;
     rc = gemm_sm100_tn(A.const_data_ptr(), B.const_data_ptr(), C.mutable_data_ptr(), M, N, K,
-                       static_cast<long>(K), static_cast<long>(K), ldc, dtype, ws_ptr, ws_bytes,
+                       lda, ldb, ldc, dtype, ws_ptr, ws_bytes,
                        static_cast<void*>(stream), &cuda_error);
   }
   raise_for(rc, cuda_error, "gemm_tn_test");
   return C;
+}
+
+// A * B^T stored through raw device pointers into several outputs of shape [M, N] with row pitch
+// `ldc` (elements).  The pointers may name peer-GPU memory mapped into this process; they are
+// not tensors on purpose (symmetric-memory handles expose peers as addresses).
+void gemm_tn_fanout(const torch::Tensor A, const torch::Tensor B, const std::vector<int64_t>& output_ptrs,
+                    int64_t ldc) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda(), "All tensors must be CUDA tensors");
+  TORCH_CHECK(A.device() == B.device(), "All tensors must be on the same device");
+  TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "All tensors must be contiguous");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "Both tensors must be 2D (matrix) tensors");
+  TORCH_CHECK(A.size(1) == B.size(1), "Inner dimensions of A and B must match (A: ", A.size(1),
+              ", B: ", B.size(1), ")");
+  TORCH_CHECK(B.scalar_type() == A.scalar_type(), "A and B must have the same dtype");
+  TORCH_CHECK(!output_ptrs.empty() && output_ptrs.size() <= 8, "between 1 and 8 outputs");
+  const int dtype = dtype_code(A);
+  std::vector<void*> outs;
+  for (int64_t ptr : output_ptrs) outs.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)));
+  c10::cuda::CUDAGuard guard(A.device());
+  cudaStream_t stream = c10::cuda::getCurrentCUDAStream(A.device().index()).stream();
+  int cuda_error = 0;
+  int rc;
+  {
+    pybind11::gil_scoped_release release;
+    rc = gemm_sm100_tn_fanout(A.const_data_ptr(), B.const_data_ptr(), outs.data(), static_cast<int>(outs.size()),
+                              static_cast<int>(A.size(0)), static_cast<int>(B.size(0)), static_cast<int>(A.size(1)),
+                              static_cast<long>(A.size(1)), static_cast<long>(A.size(1)), static_cast<long>(ldc),
+                              dtype, static_cast<void*>(stream), &cuda_error);
+  }
+  raise_for(rc, cuda_error, "gemm_tn_fanout");
 }
 
 // Waits for the current device and raises if a kernel reported a timed-out wait.
@@ -107,6 +143,8 @@ std::string describe_config(int index) {
 PYBIND11_MODULE(_C, m) {
   m.def("gemm_tn_test", &gemm_tn_test, "GEMM transpose-normal test function", pybind11::arg("A"),
         pybind11::arg("B"), pybind11::arg("C"));
+  m.def("gemm_tn_fanout", &gemm_tn_fanout, "A * B^T stored into several outputs given as device addresses",
+        pybind11::arg("A"), pybind11::arg("B"), pybind11::arg("output_ptrs"), pybind11::arg("ldc"));
   m.def("device_status", &device_status,
         "Synchronise the current device and raise if a GEMM kernel reported a failed wait");
   m.def("set_option", &set_option, pybind11::arg("name"), pybind11::arg("value"));

@@ -28,6 +28,7 @@ except ImportError as exc:  # pragma: no cover - exercised only on an unbuilt tr
 import torch as _torch
 
 gemm_tn_test = _C.gemm_tn_test
+gemm_tn_fanout = _C.gemm_tn_fanout
 device_status = _C.device_status
 set_option = _C.set_option
 describe_config = _C.describe_config
@@ -47,9 +48,9 @@ def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" 
     return gemm_tn_test(A, B, out)
 
 
-from .nsplit import NSplitPlan, gemm_tn_nsplit, shard_rows  # noqa: E402
+from .nsplit import FusedNSplit, NSplitPlan, gemm_tn_nsplit, shard_rows  # noqa: E402
 
 __all__ = [
-    "gemm_tn_test", "gemm_tn", "gemm_tn_nsplit", "NSplitPlan", "shard_rows", "device_status",
+    "gemm_tn_test", "gemm_tn", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
     "set_option", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

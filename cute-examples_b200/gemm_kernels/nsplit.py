@@ -129,6 +129,47 @@ def gemm_tn_nsplit(A: torch.Tensor, B_shard: torch.Tensor, C: torch.Tensor,
     return C
 
 
+class FusedNSplit:
+    """Column-sharded GEMM with the all-gather of C folded into the GEMM epilogue.
+
+    Every rank owns a full ``C[M, N]`` in symmetric memory (same allocation on every GPU, mapped
+    into every process).  Rank g computes its column slab ``A @ B_g.T`` once and its epilogue
+    stores every finished tile into all G copies of C (one TMA store per GPU per tile: the local
+    one and G-1 over NVLink), at column offset ``g * N/G``.  No staging slab, no NCCL all-gather,
+    no re-stride copy; one cross-GPU barrier before the step (nobody still reads the previous C)
+    and one after it (everybody's stores have landed).  Peer memory is only ever written, never
+    loaded from.
+    """
+
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.M, self.N = M, N
+        self.lo, self.hi = shard_rows(N, self.world, self.rank)
+        self.C = symm_mem.empty((M, N), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.C, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != self.world:
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected number of buffers")
+        # own copy first: the local store does not wait behind the link
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        self.output_ptrs = [ptrs[r] + self.lo * self.C.element_size() for r in order]
+
+    def __call__(self, A: torch.Tensor, B_shard: torch.Tensor) -> torch.Tensor:
+        from . import gemm_tn_fanout
+
+        if tuple(A.shape) != (self.M, B_shard.shape[1]) or B_shard.shape[0] != self.hi - self.lo:
+            raise ValueError(f"expected A [{self.M}, K] and B shard [{self.hi - self.lo}, K], got "
+                             f"{tuple(A.shape)} and {tuple(B_shard.shape)}")
+        self.handle.barrier(channel=0)
+        gemm_tn_fanout(A, B_shard, self.output_ptrs, self.N)
+        self.handle.barrier(channel=1)
+        return self.C
+
+
 _COMM_STREAMS: dict = {}
 
 

@@ -55,6 +55,18 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
                   long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
                   int* cuda_error_out);
 
+/* C = A * B^T stored into `num_outputs` (1..8) output matrices at once: the epilogue issues one
+ * TMA store per output for every finished tile.  All outputs share M, N, ldc and dtype; each
+ * pointer must be 16-byte aligned and writable from the current device (its own memory, or a
+ * peer GPU's memory mapped into this process, e.g. a symmetric-memory buffer).  This is the
+ * building block of the column-sharded multi-GPU GEMM: rank g passes, for every GPU r,
+ * `C_r + g * N_shard` with ldc = N_total, and the all-gather of C happens inside the GEMM as
+ * stores over NVLink (no staging buffer, no separate collective; the caller still needs a
+ * cross-GPU barrier before reading C).  K must be > 0.  Needs no workspace.
+ * No reference counterpart: the reference is single-GPU (one store per tile, gemm.cuh:388-394). */
+int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int num_outputs, int M, int N,
+                         int K, long lda, long ldb, long ldc, int dtype, void* cuda_stream, int* cuda_error_out);
+
 /* Same product C = A * B^T as gemm_sm100_tn, for hosts that have no way to hand this library
  * scratch memory and must not see it allocate any: an operator plugged into a serving stack
  * that owns the whole device through its own pool and passes only input and output buffers, a
@@ -129,6 +141,14 @@ int gemm_sm100_select_config(int M, int N, int K, int dtype);
  * The reference has no tracing in code; its profiler.py is a bare launch for Nsight
  * (kernels/tests/profiler.py:1-12). */
 int gemm_sm100_set_trace_buffer(void* device_buffer, size_t bytes);
+
+/* Self-test of the failure path, safe to run on a shared GPU: launches one warp that waits, with
+ * the same bounded wait the GEMM kernels use, on a barrier nothing ever arrives on.  After the
+ * "timeout_ms" limit the wait gives up, the kernel records status word 0x7e57 and returns;
+ * gemm_sm100_device_status then reports GEMM_SM100_ERR_DEVICE_TIMEOUT and the context stays
+ * usable.  (The reference's waits are unbounded, gemm.cuh:75-78, 91-94: a lost arrival hangs the
+ * GPU.) */
+int gemm_sm100_selftest_wait_timeout(void* cuda_stream, int* cuda_error_out);
 
 /* Static, human-readable name of a return code. */
 const char* gemm_sm100_error_string(int code);

@@ -46,6 +46,8 @@ def load_capi() -> ctypes.CDLL:
     I, L, P, Z = ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_size_t
     lib.gemm_sm100_tn.argtypes = [P, P, P, I, I, I, L, L, L, I, P, Z, P, ctypes.POINTER(I)]
     lib.gemm_sm100_tn.restype = I
+    lib.gemm_sm100_tn_fanout.argtypes = [P, P, ctypes.POINTER(P), I, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]
+    lib.gemm_sm100_tn_fanout.restype = I
     lib.gemm_sm100_tn_static_scratch.argtypes = [P, P, P, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]
     lib.gemm_sm100_tn_static_scratch.restype = I
     lib.gemm_sm100_static_scratch_capacity.argtypes = []
@@ -62,6 +64,8 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_describe_config.restype = I
     lib.gemm_sm100_select_config.argtypes = [I, I, I, I]
     lib.gemm_sm100_select_config.restype = I
+    lib.gemm_sm100_selftest_wait_timeout.argtypes = [P, ctypes.POINTER(I)]
+    lib.gemm_sm100_selftest_wait_timeout.restype = I
     lib.gemm_sm100_set_trace_buffer.argtypes = [P, Z]
     lib.gemm_sm100_set_trace_buffer.restype = I
     lib.gemm_sm100_error_string.argtypes = [I]

@@ -256,6 +256,50 @@ def test_split_k_rejects_missing_workspace(capi):
     assert rc == 7          # GEMM_SM100_ERR_WORKSPACE, nothing launched
 
 
+# ------------------------------------------------------------ several outputs
+@pytest.mark.parametrize("shape", [(512, 1024, 320), (300, 520, 72), (256, 256, 64)])
+@pytest.mark.parametrize("num_outputs", [1, 3, 8])
+def test_fanout_writes_every_output(gk, shape, num_outputs):
+    """The store-to-every-GPU epilogue, exercised on one GPU: the outputs are column slabs of
+    separate wide buffers (as the column-sharded multi-GPU GEMM lays them out)."""
+    M, N, K = shape
+    A, B = oracle.make_inputs(M, N, K, 95)
+    wide = [torch.full((M, 3 * N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(num_outputs)]
+    ptrs = [w.data_ptr() + (N if i % 2 else 2 * N) * 2 for i, w in enumerate(wide)]
+    gk.gemm_tn_fanout(A.cuda(), B.cuda(), ptrs, 3 * N)
+    gk.device_status()
+    single = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A.cuda(), B.cuda(), single)
+    gk.device_status()
+    assert_close(single.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    for i, w in enumerate(wide):
+        off = N if i % 2 else 2 * N
+        assert torch.equal(w[:, off:off + N].view(torch.int16), single.view(torch.int16))
+        rest = torch.cat([w[:, :off], w[:, off + N:]], dim=1)
+        assert torch.isnan(rest).all()           # nothing outside the slab was written
+
+
+def test_bounded_wait_gives_up_and_context_survives(capi):
+    """Failure detection without a GPU fault: a wait on a barrier nobody arrives on runs into
+    its (short) limit, the kernel returns, the host reads the status, later launches work."""
+    import time
+
+    assert capi.gemm_sm100_set_option(b"timeout_ms", 50) == 0
+    try:
+        err = ctypes.c_int(0)
+        t0 = time.perf_counter()
+        assert capi.gemm_sm100_selftest_wait_timeout(None, ctypes.byref(err)) == 0
+        rc, word = capi_status(capi)                  # synchronises
+        waited = time.perf_counter() - t0
+        assert rc == 6 and word == 0x7E57             # GEMM_SM100_ERR_DEVICE_TIMEOUT, self-test code
+        assert 0.04 <= waited < 20.0
+        assert capi_status(capi) == (0, 0)            # the word was cleared
+    finally:
+        capi.gemm_sm100_set_option(b"timeout_ms", 2000)
+    A, B = oracle.make_inputs(256, 256, 128, 64)
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
 def test_deterministic(capi):
     A, B = oracle.make_inputs(2048, 2048, 1024, 62)
     C1 = run_capi(capi, A, B)
