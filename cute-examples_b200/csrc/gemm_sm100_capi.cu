@@ -57,7 +57,6 @@ struct DeviceState {
   int max_ctas[kNumConfigs][2] = {};   // persistent grid limit per config and dtype
   bool attr_set[kNumConfigs][2] = {};
   bool fanout_attr_set[2][2] = {};
-  bool pf_attr_set[kNumConfigs][2] = {};
 };
 
 std::mutex g_mutex;
@@ -67,7 +66,7 @@ long g_opt_timeout_ms = 2000;
 long g_opt_max_ctas = 0;
 long g_opt_debug_flags = 0;
 long g_opt_group_m = 0;
-long g_opt_l2_prefetch = 0;   // K blocks of L2 prefetch distance (0 = off)
+long g_opt_k_rotate = 0;      // 0 never (default: measured no gain on B200), 1 always, -1 when there is a single tile row
 long g_opt_split_k = -1;     // -1 automatic, 0 never, 1 whenever the configuration allows it
 unsigned long long* g_trace_ptr = nullptr;   // device buffer for per-CTA trace records, or null
 size_t g_trace_bytes = 0;
@@ -99,16 +98,15 @@ int get_encoder(int* cuda_error_out) {
 // Tensor map of a row-major 2-D array of 16-bit elements: `rows` x `cols`, pitch `ld`
 // elements, box `box_rows` x 64 columns, 128-byte swizzle (64 x 2 B = one swizzle row).
 int encode_2d(CUtensorMap* map, const void* base, int dtype, long rows, long cols, long ld,
-              int box_rows, int* cuda_error_out, int box_cols = 64) {
+              int box_rows, int* cuda_error_out) {
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem_strides[2] = {1u, 1u};
   const CUtensorMapDataType dt =
       dtype == GEMM_SM100_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_cuda_error(cuda_error_out, cudaErrorInvalidValue);
   return GEMM_SM100_OK;
@@ -287,7 +285,9 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
   tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
   tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
-  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : (Cfg::kCtaGroup == 2 ? 8 : 16);
+  // Rasterisation group: 16 tile rows when the problem has that many (measured best from 8192
+  // to 32768 rows: the A panel of a group is reused by more B tiles), else 8.
+  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : (tp.m_tiles >= 16 ? 16 : 8);
   tp.status = st.status_ptr;
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
   tp.trace = nullptr;
@@ -295,6 +295,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   tp.sk_flags = nullptr;
   tp.sk_partials = nullptr;
   tp.sk_rows = 128;
+  tp.k_rotate = (g_opt_k_rotate > 0 || (g_opt_k_rotate < 0 && tp.m_tiles == 1 && !plan.split_k)) ? 1 : 0;
   if (plan.split_k) {
     tp.sk_flags = static_cast<unsigned int*>(workspace);
     tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
@@ -334,36 +335,6 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   attrs[0].val.clusterDim.z = 1;
   cfg.attrs = attrs;
   cfg.numAttrs = 1;
-  tp.pf_blocks = 0;
-  if (g_opt_l2_prefetch > 0 && !debug) {
-    PrefetchMaps pf;
-    rc = encode_2d(&pf.maps[0], p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out, 256);
-    if (rc) return rc;
-    rc = encode_2d(&pf.maps[1], p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out, 256);
-    if (rc) return rc;
-    tp.pf_blocks = static_cast<int>(g_opt_l2_prefetch);
-    auto pf_kernel = gemm_tn_prefetch_kernel<Cfg, false>;
-    if constexpr (kCfgIndex == kSplitKConfig) {
-      if (plan.split_k) pf_kernel = gemm_tn_prefetch_kernel<Cfg, true>;
-    }
-    {
-      std::lock_guard<std::mutex> lock(g_mutex);
-      if (!st.pf_attr_set[kCfgIndex][dt]) {
-        e = cudaFuncSetAttribute(gemm_tn_prefetch_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::kSmemBytes);
-        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-        if constexpr (kCfgIndex == kSplitKConfig) {
-          e = cudaFuncSetAttribute(gemm_tn_prefetch_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   Cfg::kSmemBytes);
-          if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-        }
-        st.pf_attr_set[kCfgIndex][dt] = true;
-      }
-    }
-    e = cudaLaunchKernelEx(&cfg, pf_kernel, map_a, map_b, map_c, pf, tp);
-    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-    return GEMM_SM100_OK;
-  }
   e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
@@ -393,7 +364,7 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
   tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
   tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
   tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
-  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : 8;
+  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : (tp.m_tiles >= 16 ? 16 : 8);
   tp.status = st.status_ptr;
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
   tp.trace = nullptr;
@@ -401,7 +372,7 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
   tp.sk_flags = nullptr;
   tp.sk_partials = nullptr;
   tp.sk_rows = 128;
-  tp.pf_blocks = 0;
+  tp.k_rotate = 0;
 
   CUtensorMap map_a, map_b;
   OutputMaps out;
@@ -653,9 +624,9 @@ int gemm_sm100_set_option(const char* name, long value) {
     g_opt_debug_flags = value;
     return GEMM_SM100_OK;
   }
-  if (std::strcmp(name, "l2_prefetch") == 0) {
-    if (value < 0 || value > 256) return GEMM_SM100_ERR_BAD_OPTION;
-    g_opt_l2_prefetch = value;
+  if (std::strcmp(name, "k_rotate") == 0) {
+    if (value < -1 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_k_rotate = value;
     return GEMM_SM100_OK;
   }
   if (std::strcmp(name, "split_k") == 0) {

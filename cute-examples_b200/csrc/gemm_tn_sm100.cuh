@@ -59,9 +59,10 @@ struct TileParams {
   unsigned int* sk_flags;          // zeroed before the launch
   float* sk_partials;              // grid x (sk_rows x kBlockN) floats
   int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
-  // Optional L2 prefetch of the operands in runs of 4 K blocks (512 contiguous bytes per row), so
-  // that DRAM sees longer bursts than the 128-byte rows of the shared-memory tiles.
-  int pf_blocks;                   // how many K blocks ahead of the loads the prefetch runs (0 = off)
+  // Start every tile's K loop at a different K block (wrapping around).  Used when each B tile is
+  // read exactly once (a single tile row, the memory-bound small-M case): the CTAs then stream
+  // different column offsets at any moment, which spreads the requests over the DRAM channels.
+  int k_rotate;
 };
 
 // Experiment switches (results are garbage with any of them set).
@@ -278,8 +279,7 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
 // happens in the epilogue as TMA stores over NVLink).
 template <class Cfg, bool kDebug, bool kSplitK>
 __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
-                                             const CUtensorMap* tmap_c, const int num_c, const TileParams& p,
-                                             const CUtensorMap* pf_maps = nullptr) {
+                                             const CUtensorMap* tmap_c, const int num_c, const TileParams& p) {
   constexpr int G = Cfg::kCtaGroup;
   constexpr int kStages = Cfg::kStages;
   unsigned long long* trace = nullptr;
@@ -372,7 +372,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
       Segment seg;
       bool have = work.next(seg);
-      int kb = seg.kb0, row_a = 0, row_b = 0;
+      int kb = seg.kb0, row_a = 0, row_b = 0, rot = 0;
       bool seg_start = true;
       bool ok = true;
       long long stall = 0;
@@ -385,6 +385,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             tile_coords(seg.tile, p, m_tile, n_tile);
             row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
             row_b = n_tile * Cfg::kBlockN + (int)cta_rank * Cfg::kBRows;
+            rot = p.k_rotate ? (int)(((long long)seg.tile * k_blocks) / num_tiles) : 0;
             seg_start = false;
           }
           long long t0 = 0;
@@ -395,24 +396,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           }
           if constexpr (kDebug)
             if (trace) stall += clock64() - t0;
-          const int x = kb * Cfg::kBlockK;
-          if (pf_maps != nullptr && p.pf_blocks > 0 && issuer) {
-            // Every 4th K block (and at the start of a segment) pull the next run of 4 K blocks
-            // of this tile's A and B rows into L2: pf_maps[0] / [1] have 256-element-wide boxes.
-            const bool at_start = kb == seg.kb0;
-            if (at_start || (kb & 3) == 0) {
-              const int first = at_start ? (kb & ~3) : ((kb & ~3) + p.pf_blocks);
-              const int last = (kb & ~3) + p.pf_blocks;
-              for (int b = first; b <= last; b += 4) {
-                if (b < seg.kb1) {
-                  tma_prefetch_l2_2d(pf_maps, b * Cfg::kBlockK, row_a);
-#pragma unroll
-                  for (int h = 0; h < Cfg::kHalves; ++h)
-                    tma_prefetch_l2_2d(pf_maps + 1, b * Cfg::kBlockK, row_b + h * Cfg::kMmaN);
-                }
-              }
-            }
-          }
+          int kb_phys = kb + rot;                  // which K block this step loads (order is free)
+          if (kb_phys >= k_blocks) kb_phys -= k_blocks;
+          const int x = kb_phys * Cfg::kBlockK;
           if (issuer) {
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
             tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
@@ -720,19 +706,6 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
   gemm_tn_body<Cfg, kDebug, kSplitK>(tmap_a, tmap_b, &tmap_c, 1, p);
-}
-
-// Operand maps with 256-element-wide boxes, used only for L2 prefetch ([0] = A, [1] = B).
-struct PrefetchMaps {
-  CUtensorMap maps[2];
-};
-
-template <class Cfg, bool kSplitK = false>
-__global__ void __launch_bounds__(Cfg::kThreads, 1)
-gemm_tn_prefetch_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PrefetchMaps pf,
-                        const TileParams p) {
-  gemm_tn_body<Cfg, false, kSplitK>(tmap_a, tmap_b, &tmap_c, 1, p, pf.maps);
 }
 
 // Self-test of the bounded wait: one warp waits on a barrier that nothing ever arrives on.  The

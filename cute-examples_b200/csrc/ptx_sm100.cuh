@@ -167,13 +167,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
   }
 }
 
-// 2-D tiled prefetch of a box into L2 (no shared-memory destination, no completion signal).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
-               : "memory");
-}
-
 // 2-D tiled store, shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int32_t x,
                                              int32_t y) {

@@ -119,7 +119,8 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  * otherwise an index reported by gemm_sm100_describe_config), "timeout_ms" (bound of each
  * device-side wait, default 2000), "max_ctas" (0 = all SMs; caps the persistent grid),
  * "split_k" (-1 = automatic, 0 = never, 1 = whenever the chosen configuration has a K-split
- * variant), "group_m" (0 = default; tile rows per rasterisation group).  Set them before
+ * variant), "group_m" (0 = default; tile rows per rasterisation group), "k_rotate" (0 = off, the default; 1 = on; -1 = on for a single tile row:
+ * start each tile's K loop at a different K block).  Set them before
  * asking gemm_sm100_workspace_bytes, which depends on them.
  * The reference's equivalents are compile-time constants (gemm.cuh:420-451). */
 int gemm_sm100_set_option(const char* name, long value);

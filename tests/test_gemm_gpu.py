@@ -38,6 +38,8 @@ def _reset_options(capi):
     capi.gemm_sm100_set_option(b"tile_config", -1)
     capi.gemm_sm100_set_option(b"max_ctas", 0)
     capi.gemm_sm100_set_option(b"split_k", -1)
+    capi.gemm_sm100_set_option(b"k_rotate", -1)
+    capi.gemm_sm100_set_option(b"group_m", 0)
 
 
 def run_capi(capi, A, B, prefill=float("nan")):
@@ -277,6 +279,31 @@ def test_fanout_writes_every_output(gk, shape, num_outputs):
         assert torch.equal(w[:, off:off + N].view(torch.int16), single.view(torch.int16))
         rest = torch.cat([w[:, :off], w[:, off + N:]], dim=1)
         assert torch.isnan(rest).all()           # nothing outside the slab was written
+
+
+@pytest.mark.parametrize("config", [0, 1, 2, 3])
+@pytest.mark.parametrize("shape", [(128, 2048, 4096), (16, 1000, 2056), (512, 768, 640)])
+def test_rotated_k_loop(capi, config, shape):
+    """Every tile starts its K loop at a different K block and wraps around: all K blocks must
+    still be visited exactly once (integer case: exact; normal case: tolerance)."""
+    M, N, K = shape
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"k_rotate", 1)
+    A, B = oracle.make_inputs(M, N, K, 97)
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    At, Bt = oracle.make_ternary_inputs(M, N, 256, 98)
+    Ct = run_capi(capi, At, Bt)
+    assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+@pytest.mark.parametrize("group_m", [1, 3, 16, 64])
+def test_rasterisation_groups(capi, group_m):
+    M, N, K = 2304, 1280, 128          # 9 x 5 pair tiles of 256 x 256: ragged last group
+    capi.gemm_sm100_set_option(b"tile_config", 0)
+    capi.gemm_sm100_set_option(b"group_m", group_m)
+    At, Bt = oracle.make_ternary_inputs(M, N, K, 99)
+    Ct = run_capi(capi, At, Bt)
+    assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
 
 
 def test_bounded_wait_gives_up_and_context_survives(capi):
