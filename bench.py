@@ -8,7 +8,9 @@ batch:
   * N = 1: the square bf16 GEMM M=N=K=8192 (BASELINE config 2; operands ~N(0,1)/sqrt(K), seed 1).
   * N > 1: the large GEMM M=N=K=32768 (BASELINE config 5, seed 4) with B sharded by rows over the
     ranks, every rank computing its column slab of C and the slabs assembled on every rank by
-    an NCCL all-gather: strong scaling, `value` = 2*M*N*K / (max over ranks of the step time).
+    the GEMM epilogue itself (stores to every GPU's C over NVLink; `--nsplit nccl` selects the
+    NCCL all-gather path instead): strong scaling, `value` = 2*M*N*K / (max over ranks of the
+    step time).
 `value` is timed with CUDA events on the launching stream, operands resident in HBM.
 `e2e` is the same step through the public Python entry point with pinned HOST operands and a
 HOST result: host->device copies of A and B and the device->host copy of C are inside the
@@ -245,7 +247,7 @@ def run_reference(args, rank):
     else:
         M = N = K = 32768
         seed, workload = 4, f"cfg5 bf16 GEMM M=N=K=32768, N-split over {args.gpus} GPUs + all-gather of C"
-    rows = 1024 if args.gpus == 1 else 64
+    rows = 1024 if args.gpus == 1 else 256
     A, B = oracle.make_inputs(rows, N, K, seed, torch.bfloat16)
     for _ in range(min(args.warmup, 2)):
         oracle.reference_matmul_fp32(A, B)
@@ -357,9 +359,30 @@ def run_multi(args):
     A = (torch.randn((M, K), generator=g, device=device, dtype=torch.float32) / K ** 0.5).to(dtype)
     gb = torch.Generator(device=device).manual_seed(4000 + rank)
     B_shard = (torch.randn((hi - lo, K), generator=gb, device=device, dtype=torch.float32) / K ** 0.5).to(dtype)
-    C = torch.empty((M, N), dtype=dtype, device=device)
-    plan = gk.NSplitPlan.create(M, N, world, dtype, device, num_panels=args.panels)
-    step = lambda: gk.gemm_tn_nsplit(A, B_shard, C, plan=plan)  # noqa: E731
+    # Default: the all-gather of C folded into the GEMM epilogue (stores to every GPU's C over
+    # NVLink, symmetric memory).  --nsplit nccl: per-panel GEMM + NCCL all-gather + re-stride copy.
+    mode = args.nsplit
+    fused = None
+    if mode in ("auto", "fused"):
+        try:
+            fused = gk.FusedNSplit(M, N, dtype, device)
+            mode = "fused"
+        except Exception as exc:  # symmetric memory unavailable on this box
+            if args.nsplit == "fused":
+                raise
+            print(f"[bench] symmetric memory unavailable ({exc!r}); using the NCCL all-gather path", file=sys.stderr)
+            mode = "nccl"
+    if mode == "fused":
+        C = fused.C
+        launches_per_step = 1
+        step = lambda: fused(A, B_shard)  # noqa: E731
+        how = "all-gather of C fused into the GEMM epilogue (TMA stores to every GPU's C over NVLink)"
+    else:
+        C = torch.empty((M, N), dtype=dtype, device=device)
+        plan = gk.NSplitPlan.create(M, N, world, dtype, device, num_panels=args.panels)
+        launches_per_step = plan.num_panels
+        step = lambda: gk.gemm_tn_nsplit(A, B_shard, C, plan=plan)  # noqa: E731
+        how = f"NCCL all-gather of C, {plan.num_panels} row panels overlapped with the GEMM"
 
     def barrier():
         dist.barrier(device_ids=[local])
@@ -382,7 +405,7 @@ def run_multi(args):
     def e2e_step():
         A.copy_(Ah, non_blocking=True)
         B_shard.copy_(Bh, non_blocking=True)
-        gk.gemm_tn_nsplit(A, B_shard, C, plan=plan)
+        step()
         Ch.copy_(C, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 3))
@@ -402,19 +425,19 @@ def run_multi(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"cfg5 bf16 TN GEMM M=N=K=32768, B row-sharded over {world} GPUs, "
-                                   f"NCCL all-gather of C, {plan.num_panels} row panels", "M": M, "N": N, "K": K,
+            "config": {"workload": f"cfg5 bf16 TN GEMM M=N=K=32768, B row-sharded over {world} GPUs, {how}",
+                       "M": M, "N": N, "K": K, "nsplit_mode": mode,
                        "per_gpu_tflops": round(per_gpu, 2),
                        "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"},
             "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (M * K + (hi - lo) * K) * 2, "d2h_bytes_per_step": M * N * 2,
                     "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
-            "gpu_launches": args.steps * plan.num_panels,
+            "gpu_launches": args.steps * launches_per_step,
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": peak, "unit": "TFLOP/s",
                          "frac": round(per_gpu / peak, 4), "traffic": None,
                          "peak_source": f"{peak_src}:bf16_tflops_sustained", "kernel": "gemm_sm100::gemm_tn_kernel",
-                         "note": "per-GPU TFLOP/s of the whole step (GEMM panels + overlapped all-gather)"},
+                         "note": "per-GPU TFLOP/s of the whole step (GEMM + exchange of C + barriers)"},
             "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
@@ -429,6 +452,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--panels", type=int, default=8)
+    ap.add_argument("--nsplit", default="auto", choices=["auto", "fused", "nccl"],
+                    help="multi-GPU exchange of C: fused into the GEMM epilogue (default) or NCCL all-gather")
     ap.add_argument("--no-shapes", action="store_true", help="skip the secondary BASELINE shapes")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

@@ -48,7 +48,7 @@ def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" 
     return gemm_tn_test(A, B, out)
 
 
-from .nsplit import FusedNSplit, NSplitPlan, gemm_tn_nsplit, shard_rows  # noqa: E402
+from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, shard_rows  # noqa: E402
 
 __all__ = [
     "gemm_tn_test", "gemm_tn", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",

@@ -129,6 +129,16 @@ def gemm_tn_nsplit(A: torch.Tensor, B_shard: torch.Tensor, C: torch.Tensor,
     return C
 
 
+def fanout_pointers(buffer_ptrs, rank: int, column_offset: int, element_size: int) -> list:
+    """Device addresses rank `rank` stores its column slab to: the same column offset inside every
+    GPU's C, its own copy first (the local store does not wait behind the link)."""
+    world = len(buffer_ptrs)
+    if not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} for {world} buffers")
+    order = [rank] + [r for r in range(world) if r != rank]
+    return [int(buffer_ptrs[r]) + column_offset * element_size for r in order]
+
+
 class FusedNSplit:
     """Column-sharded GEMM with the all-gather of C folded into the GEMM epilogue.
 
@@ -154,9 +164,9 @@ class FusedNSplit:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         if len(ptrs) != self.world:
             raise RuntimeError("symmetric memory rendezvous returned an unexpected number of buffers")
-        # own copy first: the local store does not wait behind the link
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
-        self.output_ptrs = [ptrs[r] + self.lo * self.C.element_size() for r in order]
+        if self.world > 8:
+            raise ValueError("the fused exchange stores to at most 8 GPUs")
+        self.output_ptrs = fanout_pointers(ptrs, self.rank, self.lo, self.C.element_size())
 
     def __call__(self, A: torch.Tensor, B_shard: torch.Tensor) -> torch.Tensor:
         from . import gemm_tn_fanout

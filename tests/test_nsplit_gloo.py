@@ -102,3 +102,16 @@ def test_shard_rows():
         shard_rows(48, 4, 0)       # 12 columns per rank: not a multiple of 8
     with pytest.raises(ValueError):
         shard_rows(64, 2, 2)
+
+
+def test_fanout_pointers():
+    from gemm_kernels import fanout_pointers, shard_rows
+
+    bufs = [0x1000_0000, 0x2000_0000, 0x3000_0000, 0x4000_0000]
+    lo, _ = shard_rows(32768, 4, 2)
+    ptrs = fanout_pointers(bufs, 2, lo, 2)
+    assert ptrs[0] == 0x3000_0000 + lo * 2                       # own copy first
+    assert sorted(p - lo * 2 for p in ptrs) == bufs              # every GPU exactly once
+    assert all(p % 16 == 0 for p in ptrs)                        # slab starts stay 16-byte aligned
+    with pytest.raises(ValueError):
+        fanout_pointers(bufs, 4, 0, 2)
