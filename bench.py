@@ -40,6 +40,10 @@ sys.path.insert(0, str(REPO / "cute-examples_b200"))
 
 import torch  # noqa: E402
 
+# DRAM traffic of one launch of the N=1 workload (M=N=K=8192), from the ncu capture summarised in
+# profiles/gemm_tn_kernel_256x512_bf16_8192cubed_ncu_full.md (mean of two launches).
+NCU_DRAM_BYTES_PER_LAUNCH_8192 = 985_000_000
+
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
 
@@ -331,7 +335,10 @@ def run_single(args):
         "gpu_launches": args.steps,
         "clocks": clk.summary(),
         "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
-                     "frac": round(tflops / peak, 4), "traffic": None,
+                     "frac": round(tflops / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH_8192,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this "
+                                       "workload (profiles/gemm_tn_kernel_256x512_bf16_8192cubed_ncu_full.md); "
+                                       "algorithmic bytes 4.03e8",
                      "peak_source": f"{peak_src}:{peak_key}", "kernel": "gemm_sm100::gemm_tn_kernel",
                      "flops_per_launch": gemm_flops(M, N, K)},
         "cpu_baseline": cpu,

@@ -589,18 +589,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           if (trace) stall += clock64() - te;
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + slot * Cfg::kMmaN;
-#pragma unroll 1
-        for (int c = cg; c < kChunks; c += kColGroups) {
-          uint32_t v0[32], v1[32];
-          tmem_ld_32x32(taddr + c * Cfg::kEpiCols, v0);
-          tmem_ld_32x32(taddr + c * Cfg::kEpiCols + 32, v1);
-          tmem_ld_wait();
-          if (c + kColGroups >= kChunks) {
-            // All of this warp's reads of the slot are done: hand it back to the MMA issuer.
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * slot);
-          }
+        // Everything that happens to one 32-row x 64-column chunk once it sits in registers.
+        auto finish_chunk = [&](const int c, uint32_t (&v0)[32], uint32_t (&v1)[32]) {
           if constexpr (kSplitK) {
             const int piece0 = (h * kChunks + c) * 16;       // first 16-byte piece of this chunk
             if (writes_partial) {
@@ -614,7 +604,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
                                                                __uint_as_float(v[2]), __uint_as_float(v[3]));
                 }
               }
-              continue;                                        // nothing goes to C from this segment
+              return;                                          // nothing goes to C from this segment
             }
             if (reduces && row_live) {
               for (int w = 0; w < writer_count; ++w) {
@@ -662,6 +652,37 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             }
             if constexpr (Cfg::kEpiBufs == 2) buf ^= 1u;
           }
+        };
+        constexpr int kPerWarp = kChunks / kColGroups;       // chunks of one slot this warp drains
+        if constexpr (kPerWarp == 2 && !kSplitK) {
+          // Drain both chunks into registers first and hand the slot back at once: the MMA
+          // issuer restarts ~2 chunk-stores earlier (the double-width tile has no spare slot).
+          uint32_t a0[32], a1[32], b0[32], b1[32];
+          tmem_ld_32x32(taddr + cg * Cfg::kEpiCols, a0);
+          tmem_ld_32x32(taddr + cg * Cfg::kEpiCols + 32, a1);
+          tmem_ld_32x32(taddr + (cg + kColGroups) * Cfg::kEpiCols, b0);
+          tmem_ld_32x32(taddr + (cg + kColGroups) * Cfg::kEpiCols + 32, b1);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * slot);
+          finish_chunk(cg, a0, a1);
+          finish_chunk(cg + kColGroups, b0, b1);
+        } else {
+#pragma unroll 1
+          for (int c = cg; c < kChunks; c += kColGroups) {
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32(taddr + c * Cfg::kEpiCols, v0);
+            tmem_ld_32x32(taddr + c * Cfg::kEpiCols + 32, v1);
+            tmem_ld_wait();
+            if (c + kColGroups >= kChunks) {
+              // All of this warp's reads of the slot are done: hand it back to the MMA issuer.
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * slot);
+            }
+            finish_chunk(c, v0, v1);
+          }
         }
       }
       if constexpr (kSplitK) {
@@ -673,7 +694,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
         }
       }
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    if (lane == 0) tma_store_wait_read<0>();   // smem may go once it has been read; the writes finish on their own
     __syncwarp();
     if constexpr (kDebug)
       if (trace && warp == 2 && lane == 0) {
