@@ -167,7 +167,9 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // pair tile: the wider the tile, the fewer bytes cross L2 -> shared memory per flop.
 constexpr int kAutoConfigs = 4;                       // candidates of the automatic choice
 constexpr double kConfigRate[kAutoConfigs] = {0.96, 1.0, 0.72, 0.5};
-constexpr int kSplitKConfig = 2;                      // the configuration that has a K-split variant
+constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
+// Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
+constexpr bool has_split_k(int config) { return config == 1 || config == 2; }
 
 struct Plan {
   int config = 0;
@@ -204,15 +206,22 @@ Plan make_plan(int M, int N, int K, int sm_count) {
     Plan cand;
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
-    double cost = static_cast<double>(waves) * block_n / rate;
+    // costs in units of (one K block of one tile column) per CTA
+    double cost = static_cast<double>(waves) * block_n * k_blocks / rate;
     const long units = tiles * k_blocks;
-    // Automatic choice: only when whole tiles would leave more than half of the SMs idle and
-    // every CTA still gets a long run of K blocks.  Forced (split_k = 1): whenever it is possible.
-    const bool can_split = i == kSplitKConfig && units >= 2;
-    const bool auto_split = g_opt_split_k < 0 && units >= slots * 8 && tiles * 2 <= slots;
+    const long ranges = units < slots ? units : slots;
+    // K-split: every CTA (pair) gets units / ranges K blocks, plus the fix-up of the cut tiles
+    // (partial tile out and in, a wait for the neighbour: about 9 K blocks' worth of time).
+    const double split_cost = static_cast<double>(units) / ranges * block_n / rate + 9.0 * block_n;
+    // Automatic choice: only when whole tiles would leave more than half of the SMs idle and every
+    // CTA still gets a long run of K blocks.  (Measured on B200: for 4096^3, 1.73 waves of
+    // 256 x 512 tiles, the K-split schedule took 111 us against 95 us for whole tiles: the three
+    // exposed epilogues per CTA pair and the lost lockstep sharing of operands cost more than the
+    // idle quarter wave.  So a bad wave count alone does not select it.)
+    const bool auto_split = g_opt_split_k < 0 && units >= slots * 16 && tiles * 2 <= slots;
+    const bool can_split = has_split_k(i) && units >= 2;
     if (can_split && (g_opt_split_k > 0 || auto_split)) {
-      const long ranges = units < slots ? units : slots;
-      cost = static_cast<double>(tiles) / ranges * block_n / rate * 1.04 + 8.0;
+      cost = split_cost;
       cand.split_k = true;
       cand.ctas = static_cast<int>(ranges * c.cta_group);
       cand.partial_rows = M < 128 ? static_cast<int>((M + 31) / 32 * 32) : 128;
@@ -235,7 +244,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   // The instrumented instantiation runs only while a trace buffer or an experiment flag is set.
   const bool debug = g_trace_ptr != nullptr || g_opt_debug_flags != 0;
   auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
-  if constexpr (kCfgIndex == kSplitKConfig) {
+  if constexpr (has_split_k(kCfgIndex)) {
     if (plan.split_k) kernel = gemm_tn_kernel<Cfg, false, true>;
   }
   constexpr int dt = kIsBf16 ? 0 : 1;
@@ -248,7 +257,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
       if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
       e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
       if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-      if constexpr (kCfgIndex == kSplitKConfig) {
+      if constexpr (has_split_k(kCfgIndex)) {
         e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemBytes);
         if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);

@@ -218,10 +218,11 @@ SPLIT_SHAPES = [
 
 
 @pytest.mark.parametrize("shape", SPLIT_SHAPES)
-def test_split_k_matches_oracle(capi, shape):
+@pytest.mark.parametrize("config", [1, 2])
+def test_split_k_matches_oracle(capi, shape, config):
     M, N, K, max_ctas = shape
     A, B = oracle.make_inputs(M, N, K, 80 + M % 5)
-    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"tile_config", config)
     capi.gemm_sm100_set_option(b"split_k", 1)
     capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
     assert capi.gemm_sm100_workspace_bytes(M, N, K, 0) > 0
@@ -232,13 +233,24 @@ def test_split_k_matches_oracle(capi, shape):
     assert torch.equal(C.view(torch.int16), C2.view(torch.int16))
 
 
+def test_split_k_automatic_choice(capi):
+    """Chosen by itself only when whole tiles would leave more than half of the SMs idle and K is
+    long; never for the BASELINE shapes (measured slower there)."""
+    assert capi.gemm_sm100_workspace_bytes(256, 512, 65536, 0) > 0
+    for shape in [(4096, 4096, 4096), (8192, 8192, 8192), (128, 28672, 8192), (1024, 1024, 1024)]:
+        assert capi.gemm_sm100_workspace_bytes(*shape, 0) == 0
+    A, B = oracle.make_inputs(256, 512, 16384, 82)
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+@pytest.mark.parametrize("config", [1, 2])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_split_k_exact_on_integers(capi, dtype):
+def test_split_k_exact_on_integers(capi, dtype, config):
     """Integer-valued sums are exact in fp32 however K is cut, so the K-split result must equal
     the unsplit one bit for bit."""
     M, N, K = 128, 1536, 256
     A, B = oracle.make_ternary_inputs(M, N, K, 81, dtype)
-    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"tile_config", config)
     capi.gemm_sm100_set_option(b"split_k", 1)
     capi.gemm_sm100_set_option(b"max_ctas", 11)
     C = run_capi(capi, A, B)
