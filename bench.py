@@ -295,6 +295,10 @@ def run_single(args):
     gk.device_status()
     ms = ms_total / args.steps
     tflops = gemm_flops(M, N, K) / ms / 1e9
+    # the clock the kernel really runs at under this load (right after the timed region, GPU warm)
+    for _ in range(3):
+        step()
+    sm_mhz_in_kernel = gk.measure_sm_clock_mhz(A, B, C)
 
     # end to end: pinned host operands in, host result out, every step
     Ah, Bh = A.cpu().pin_memory(), B.cpu().pin_memory()
@@ -333,7 +337,9 @@ def run_single(args):
         "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
         "gpu_launches": args.steps,
-        "clocks": clk.summary(),
+        "clocks": dict(clk.summary(), sm_mhz_in_kernel=round(sm_mhz_in_kernel, 0),
+                       note="sm_mhz / reasons: NVML samples during the timed region; sm_mhz_in_kernel: "
+                            "clock64 over %globaltimer inside one traced launch right after it"),
         "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(tflops / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH_8192,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this "
@@ -405,15 +411,17 @@ def run_multi(args):
     ms = t.item() / args.steps
     tflops = gemm_flops(M, N, K) / ms / 1e9
 
-    # end to end: host A and B shard in, host C out, each step
+    # end to end: host A and B shard in, host result out, each step.  Every rank ends the step
+    # with the whole C on its GPU; it reads back its own column slab, so that the ranks together
+    # bring one copy of C to the host (and pinned host memory stays bounded at 8 ranks).
     Ah, Bh = A.cpu().pin_memory(), B_shard.cpu().pin_memory()
-    Ch = torch.empty((M, N), dtype=dtype).pin_memory()
+    Ch = torch.empty((M, hi - lo), dtype=dtype).pin_memory()
 
     def e2e_step():
         A.copy_(Ah, non_blocking=True)
         B_shard.copy_(Bh, non_blocking=True)
         step()
-        Ch.copy_(C, non_blocking=True)
+        Ch.copy_(C[:, lo:hi], non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 3))
     e2e_step()
@@ -437,7 +445,8 @@ def run_multi(args):
                        "per_gpu_tflops": round(per_gpu, 2),
                        "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"},
             "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": (M * K + (hi - lo) * K) * 2, "d2h_bytes_per_step": M * N * 2,
+                    "h2d_bytes_per_step": (M * K + (hi - lo) * K) * 2 * world, "d2h_bytes_per_step": M * N * 2,
+                    "note": "bytes summed over ranks: every rank uploads A and its B shard and reads back its slab of C",
                     "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
             "gpu_launches": args.steps * launches_per_step,
             "clocks": clk.summary(),

@@ -130,6 +130,19 @@ unsigned int device_status() {
   return word;
 }
 
+// Registers (or, with an undefined tensor, removes) the device buffer the kernels write their
+// per-CTA trace records to; see gemm_sm100_set_trace_buffer.
+void set_trace_buffer(const c10::optional<torch::Tensor>& buffer) {
+  if (!buffer.has_value()) {
+    raise_for(gemm_sm100_set_trace_buffer(nullptr, 0), 0, "set_trace_buffer");
+    return;
+  }
+  const torch::Tensor& t = buffer.value();
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kInt64,
+              "trace buffer must be a contiguous CUDA int64 tensor");
+  raise_for(gemm_sm100_set_trace_buffer(t.data_ptr(), static_cast<size_t>(t.numel()) * 8), 0, "set_trace_buffer");
+}
+
 void set_option(const std::string& name, long value) {
   raise_for(gemm_sm100_set_option(name.c_str(), value), 0, "set_option");
 }
@@ -148,6 +161,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("device_status", &device_status,
         "Synchronise the current device and raise if a GEMM kernel reported a failed wait");
   m.def("set_option", &set_option, pybind11::arg("name"), pybind11::arg("value"));
+  m.def("set_trace_buffer", &set_trace_buffer, pybind11::arg("buffer"));
   m.def("describe_config", &describe_config, pybind11::arg("index"));
   m.def("select_config", &gemm_sm100_select_config, pybind11::arg("M"), pybind11::arg("N"),
         pybind11::arg("K"), pybind11::arg("dtype"));

@@ -31,6 +31,7 @@ gemm_tn_test = _C.gemm_tn_test
 gemm_tn_fanout = _C.gemm_tn_fanout
 device_status = _C.device_status
 set_option = _C.set_option
+set_trace_buffer = _C.set_trace_buffer
 describe_config = _C.describe_config
 select_config = _C.select_config
 workspace_bytes = _C.workspace_bytes
@@ -39,6 +40,27 @@ num_sms = _C.num_sms
 LIBRARY_PATH = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "libgemm_sm100.so")
 
 DTYPE_CODES = {_torch.bfloat16: 0, _torch.float16: 1}
+
+
+def measure_sm_clock_mhz(A: "_torch.Tensor", B: "_torch.Tensor", C: "_torch.Tensor") -> float:
+    """SM clock in MHz during one traced launch of ``gemm_tn_test(A, B, C)``: cycles (clock64)
+    over nanoseconds (%globaltimer) between kernel entry and exit, averaged over the CTAs.  This is
+    the clock the kernel really ran at; the driver-reported clock does not follow the fast
+    power-management steps of a power-capped GPU."""
+    trace = _torch.zeros(num_sms() * 16, dtype=_torch.int64, device=A.device)
+    set_trace_buffer(trace)
+    try:
+        gemm_tn_test(A, B, C)
+        _torch.cuda.synchronize(A.device)
+    finally:
+        set_trace_buffer(None)
+    t = trace.view(-1, 16).cpu()
+    used = t[:, 13] > t[:, 12]
+    if not bool(used.any()):
+        return float("nan")
+    cycles = (t[used, 10] - t[used, 0]).double()
+    ns = (t[used, 13] - t[used, 12]).double()
+    return float((cycles / ns).mean().item() * 1000.0)
 
 
 def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" = None) -> "_torch.Tensor":
@@ -52,5 +74,5 @@ from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, sh
 
 __all__ = [
     "gemm_tn_test", "gemm_tn", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
-    "set_option", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
+    "set_option", "set_trace_buffer", "measure_sm_clock_mhz", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

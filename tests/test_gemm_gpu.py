@@ -183,6 +183,46 @@ def test_guard_bands_and_strided_c(capi, config, shape):
     assert torch.all(host == sentinel), "kernel wrote outside C"
 
 
+def test_binding_argument_errors_are_runtime_errors(gk):
+    """The reference's argument checks (gemm_test.cu:15-41) raise RuntimeError through TORCH_CHECK;
+    so do these, and none of them launches anything or ends the process."""
+    z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt, device="cuda")  # noqa: E731
+    with pytest.raises(RuntimeError, match="same dtype"):
+        gk.gemm_tn_test(z(64, 64), z(64, 64, dt=torch.float16), z(64, 64))
+    with pytest.raises(RuntimeError, match="bfloat16 or float16"):
+        gk.gemm_tn_test(z(64, 64, dt=torch.float32), z(64, 64, dt=torch.float32), z(64, 64, dt=torch.float32))
+    with pytest.raises(RuntimeError, match="Inner dimensions"):
+        gk.gemm_tn_test(z(64, 64), z(64, 128), z(64, 64))
+    with pytest.raises(RuntimeError, match="2D"):
+        gk.gemm_tn_test(z(64), z(64, 64), z(64, 64))
+    with pytest.raises(RuntimeError, match="shape"):
+        gk.gemm_tn_test(z(64, 64), z(32, 64), z(64, 64))
+    with pytest.raises(RuntimeError, match="contiguous along K"):
+        gk.gemm_tn_test(z(64, 128)[:, ::2], z(64, 64), z(64, 64))
+    with pytest.raises(RuntimeError, match="unit stride"):
+        gk.gemm_tn_test(z(64, 64), z(64, 64), z(64, 128)[:, ::2])
+    with pytest.raises(RuntimeError, match="bad shape"):
+        gk.gemm_tn_test(z(64, 12), z(64, 12), z(64, 64))                 # K % 8 != 0
+    with pytest.raises(RuntimeError, match="16-byte"):
+        gk.gemm_tn_test(z(64, 72)[:, 4:68], z(64, 64), z(64, 64))        # A base 8 bytes off
+    with pytest.raises(RuntimeError, match="CUDA tensors"):
+        gk.gemm_tn_test(z(64, 64).cpu(), z(64, 64), z(64, 64))
+    gk.device_status()                                                   # context is fine
+
+
+def test_binding_accepts_row_pitched_operands(gk):
+    M, N, K = 256, 384, 192
+    A, B = oracle.make_inputs(M, N, K, 52)
+    Ap = torch.zeros((M, K + 64), dtype=torch.bfloat16, device="cuda")
+    Bp = torch.zeros((N, K + 8), dtype=torch.bfloat16, device="cuda")
+    Ap[:, :K] = A.cuda()
+    Bp[:, :K] = B.cuda()
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(Ap[:, :K], Bp[:, :K], C)
+    gk.device_status()
+    assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
 def test_binding_accepts_strided_c_view(gk):
     M, N, K = 256, 256, 128
     A, B = oracle.make_inputs(M, N, K, 51)

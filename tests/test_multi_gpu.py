@@ -1,0 +1,96 @@
+"""Column-sharded GEMM on real GPUs (2 ranks as child processes): both exchange paths must give,
+on every rank, bit for bit the C that one GPU computes alone.  Skipped with fewer than 2 GPUs."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+
+from conftest import PKG_ROOT, REPO
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    try:
+        for p in (str(REPO), str(PKG_ROOT)):
+            if p not in sys.path:
+                sys.path.insert(0, p)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        import datetime
+
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=120))
+        import gemm_kernels as gk
+        from oracle import oracle
+
+        M, N, K = 1024, 2048, 576
+        A, B = oracle.make_inputs(M, N, K, 4)
+        lo, hi = gk.shard_rows(N, world, rank)
+        Ad, Bs = A.cuda(), B[lo:hi].cuda().contiguous()
+        single = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        gk.gemm_tn_test(Ad, B.cuda(), single)
+        gk.device_status()
+        report = {}
+        # NCCL all-gather path, 3 row panels (ragged last one)
+        C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        plan = gk.NSplitPlan.create(M, N, world, torch.bfloat16, "cuda", num_panels=3)
+        for _ in range(2):
+            gk.gemm_tn_nsplit(Ad, Bs, C, plan=plan)
+        torch.cuda.synchronize()
+        report["nccl"] = torch.equal(C.view(torch.int16), single.view(torch.int16))
+        # exchange fused into the GEMM epilogue
+        try:
+            fused = gk.FusedNSplit(M, N, torch.bfloat16, torch.device("cuda", rank))
+        except Exception as exc:  # symmetric memory not available on this machine
+            report["fused"] = f"skipped: {exc!r}"[:200]
+        else:
+            fused.C.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            for _ in range(2):
+                Cf = fused(Ad, Bs)
+            torch.cuda.synchronize()
+            report["fused"] = torch.equal(Cf.view(torch.int16), single.view(torch.int16))
+        gk.device_status()
+        err = oracle.normalized_max_error(single.cpu(), oracle.reference_matmul_fp32(A, B))
+        report["oracle"] = err <= oracle.tolerance(torch.bfloat16)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, report))
+    except Exception:  # pragma: no cover
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_nsplit_two_gpus_matches_single_gpu():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    for rank in range(world):
+        rep = results[rank]
+        assert isinstance(rep, dict), rep
+        assert rep["oracle"] is True and rep["nccl"] is True, rep
+        assert rep["fused"] is True or str(rep["fused"]).startswith("skipped"), rep
