@@ -39,6 +39,19 @@ def _nvcc() -> str:
     return cand
 
 
+def _cxx() -> str:
+    """Host compiler of the torch binding.  GEMM_KERNELS_CXX overrides; otherwise the system g++ is
+    preferred over $CXX: a $CXX wrapper that re-orders the C++ standard include directories
+    (seen as /opt/gcc/bin/g++ in some images) produced a binding whose error messages with
+    integer arguments crashed inside iostream formatting."""
+    override = os.environ.get("GEMM_KERNELS_CXX")
+    if override:
+        return override
+    if Path("/usr/bin/g++").exists():
+        return "/usr/bin/g++"
+    return os.environ.get("CXX", "g++")
+
+
 def _newer(target: Path, sources: list[Path]) -> bool:
     if not target.exists():
         return False
@@ -83,7 +96,7 @@ def build_torch_binding(force: bool = False, verbose: bool = False) -> Path:
 
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     includes = ce.include_paths() + [sysconfig.get_paths()["include"], f"{cuda_home}/include"]
-    cmd = [os.environ.get("CXX", "g++"), "-O3", "-Wall", "-Wextra", "-std=c++17", "-fPIC", "-shared",
+    cmd = [_cxx(), "-O3", "-Wall", "-Wextra", "-std=c++17", "-fPIC", "-shared",
            "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H"]
     for inc in includes:
         cmd += ["-isystem", inc]

@@ -36,9 +36,7 @@ int dtype_code(const torch::Tensor& t) {
 // Checks follow the reference's order and wording where it has them (gemm_test.cu:15-41);
 // C is checked as well (the reference assumes it), tile-divisibility is not required.
 torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::Tensor C) {
-  TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "All tensors must be CUDA tensors");
-  TORCH_CHECK(A.device() == B.device() && A.device() == C.device(),
-              "All tensors must be on the same device");
+  // Shape and dtype first (these need no device), then placement.
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "Both tensors must be 2D (matrix) tensors");
   // The reference insists on contiguous operands (gemm_test.cu:18-19); rows with a larger pitch
   // are accepted here as long as K stays contiguous.
@@ -54,6 +52,9 @@ torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::
   TORCH_CHECK(C.numel() == 0 || C.stride(1) == 1, "C must have unit stride along its last dimension");
   TORCH_CHECK(A.size(0) <= INT32_MAX && B.size(0) <= INT32_MAX && A.size(1) <= INT32_MAX,
               "extents must fit in 32 bits");
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "All tensors must be CUDA tensors");
+  TORCH_CHECK(A.device() == B.device() && A.device() == C.device(),
+              "All tensors must be on the same device");
   const int M = static_cast<int>(A.size(0));
   const int N = static_cast<int>(B.size(0));
   const int K = static_cast<int>(A.size(1));

@@ -80,11 +80,28 @@ def test_empty_problem_is_a_noop(capi):
 
 
 def test_binding_rejects_bad_tensors_with_runtime_error():
+    """Shape and dtype checks of the binding need no device: wrong dtype, K mismatch, wrong rank,
+    wrong C shape, strided K all raise RuntimeError (the reference's TORCH_CHECKs,
+    gemm_test.cu:15-41), and CPU tensors are refused last."""
     import gemm_kernels as gk
 
     z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt)  # noqa: E731
     with pytest.raises(RuntimeError, match="CUDA tensors"):
         gk.gemm_tn_test(z(8, 8), z(8, 8), z(8, 8))
+    with pytest.raises(RuntimeError, match=r"Inner dimensions of A and B must match \(A: 64, B: 128\)"):
+        gk.gemm_tn_test(z(64, 64), z(64, 128), z(64, 64))
+    with pytest.raises(RuntimeError, match="same dtype"):
+        gk.gemm_tn_test(z(64, 64), z(64, 64, dt=torch.float16), z(64, 64))
+    with pytest.raises(RuntimeError, match="bfloat16 or float16"):
+        gk.gemm_tn_test(*(z(64, 64, dt=torch.float32),) * 3)
+    with pytest.raises(RuntimeError, match="2D"):
+        gk.gemm_tn_test(z(64), z(64, 64), z(64, 64))
+    with pytest.raises(RuntimeError, match="shape"):
+        gk.gemm_tn_test(z(64, 64), z(32, 64), z(64, 64))
+    with pytest.raises(RuntimeError, match="contiguous along K"):
+        gk.gemm_tn_test(z(64, 128)[:, ::2], z(64, 64), z(64, 64))
+    with pytest.raises(RuntimeError, match="unit stride"):
+        gk.gemm_tn_test(z(64, 64), z(64, 64), z(64, 128)[:, ::2])
     assert gk.gemm_tn_test is gk._C.gemm_tn_test
     # keyword names of the reference binding
     with pytest.raises(RuntimeError):
