@@ -70,9 +70,58 @@ def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" 
     return gemm_tn_test(A, B, out)
 
 
+class HostGemm:
+    """``C_host = A_host @ B_host.T`` for operands and result in (pinned) HOST memory.
+
+    The whole of B is uploaded first; A is uploaded in row panels, each panel's GEMM starts as
+    soon as its rows have arrived, and each finished panel of C goes back to the host while the
+    next panel of A is still coming in (PCIe carries both directions at once).  Device buffers
+    and streams are created once and reused; `__call__` returns after the last byte of C has
+    reached the host.  The reference has no host-memory path: its callers create operands on
+    the device (kernels/tests/gemm_test.py:23-28).
+    """
+
+    def __init__(self, M: int, N: int, K: int, dtype=_torch.bfloat16, device="cuda", panels: int = 8):
+        self.M, self.N, self.K = M, N, K
+        self.device = _torch.device(device)
+        rows = -(-M // max(1, panels))
+        self.panel_rows = max(256, -(-rows // 256) * 256) if M >= 256 else M
+        self.A = _torch.empty((M, K), dtype=dtype, device=self.device)
+        self.B = _torch.empty((N, K), dtype=dtype, device=self.device)
+        self.C = _torch.empty((M, N), dtype=dtype, device=self.device)
+        self.h2d = _torch.cuda.Stream(device=self.device)
+        self.d2h = _torch.cuda.Stream(device=self.device)
+
+    def __call__(self, A_host: "_torch.Tensor", B_host: "_torch.Tensor", C_host: "_torch.Tensor") -> "_torch.Tensor":
+        if tuple(A_host.shape) != (self.M, self.K) or tuple(B_host.shape) != (self.N, self.K) or \
+                tuple(C_host.shape) != (self.M, self.N):
+            raise ValueError("operand shapes do not match the plan")
+        compute = _torch.cuda.current_stream(self.device)
+        self.h2d.wait_stream(compute)          # the previous call's kernels are done with A and B
+        self.d2h.wait_stream(compute)
+        with _torch.cuda.stream(self.h2d):
+            self.B.copy_(B_host, non_blocking=True)
+        for r0 in range(0, self.M, self.panel_rows):
+            r1 = min(self.M, r0 + self.panel_rows)
+            with _torch.cuda.stream(self.h2d):
+                self.A[r0:r1].copy_(A_host[r0:r1], non_blocking=True)
+                arrived = _torch.cuda.Event()
+                arrived.record(self.h2d)
+            compute.wait_event(arrived)
+            gemm_tn_test(self.A[r0:r1], self.B, self.C[r0:r1])
+            done = _torch.cuda.Event()
+            done.record(compute)
+            self.d2h.wait_event(done)
+            with _torch.cuda.stream(self.d2h):
+                C_host[r0:r1].copy_(self.C[r0:r1], non_blocking=True)
+        compute.wait_stream(self.d2h)
+        compute.synchronize()
+        return C_host
+
+
 from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, shard_rows  # noqa: E402
 
 __all__ = [
-    "gemm_tn_test", "gemm_tn", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
+    "gemm_tn_test", "gemm_tn", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
     "set_option", "set_trace_buffer", "measure_sm_clock_mhz", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

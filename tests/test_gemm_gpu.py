@@ -223,6 +223,23 @@ def test_binding_accepts_row_pitched_operands(gk):
     assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
 
 
+@pytest.mark.parametrize("shape,panels", [((1024, 768, 320), 4), ((300, 264, 72), 8), ((2048, 512, 256), 3)])
+def test_host_memory_entry_point(gk, shape, panels):
+    M, N, K = shape
+    A, B = oracle.make_inputs(M, N, K, 53)
+    Ah, Bh = A.pin_memory(), B.pin_memory()
+    Ch = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    hg = gk.HostGemm(M, N, K, torch.bfloat16, "cuda", panels=panels)
+    for _ in range(2):                      # buffers and streams are reused between calls
+        out = hg(Ah, Bh, Ch)
+    gk.device_status()
+    assert out is Ch
+    assert_close(Ch, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    direct = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A.cuda(), B.cuda(), direct)
+    assert torch.equal(direct.cpu().view(torch.int16), Ch.view(torch.int16))
+
+
 def test_binding_accepts_strided_c_view(gk):
     M, N, K = 256, 256, 128
     A, B = oracle.make_inputs(M, N, K, 51)
