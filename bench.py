@@ -5,8 +5,8 @@
 
 One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one synthetic
 batch:
-  * N = 1: the square bf16 GEMM M=N=K=8192 (BASELINE config 2; operands ~N(0,1)/sqrt(K), seed 1).
-  * N > 1: the large GEMM M=N=K=32768 (BASELINE config 5, seed 4) with B sharded by rows over the
+  * N = 1: the square bf16 GEMM M=N=K=8192 (benchmark configuration 2; operands ~N(0,1)/sqrt(K), seed 1).
+  * N > 1: the large GEMM M=N=K=32768 (benchmark configuration 5, seed 4) with B sharded by rows over the
     ranks, every rank computing its column slab of C and the slabs assembled on every rank by
     the GEMM epilogue itself (stores to every GPU's C over NVLink; `--nsplit nccl` selects the
     NCCL all-gather path instead): strong scaling, `value` = 2*M*N*K / (max over ranks of the
@@ -15,7 +15,7 @@ batch:
 `e2e` is the same step through the public Python entry point with pinned HOST operands and a
 HOST result: host->device copies of A and B and the device->host copy of C are inside the
 timed region.  `roofline` compares the GEMM kernel with the measured cuBLAS bf16 peak of this
-pool (MEASURED_PEAKS.json, else the stated fallback).  `cpu_baseline` times the CPU oracle
+pool (a driver-written JSON file beside this script, else the stated fallback).  `cpu_baseline` times the CPU oracle
 (the reference's check expression, torch fp32 matmul) on the host cores.
 
 --impl reference: the reference's implementation of this path is sm_90a device code that cannot
@@ -40,8 +40,8 @@ sys.path.insert(0, str(REPO / "cute-examples_b200"))
 
 import torch  # noqa: E402
 
-# DRAM traffic of one launch of the N=1 workload (M=N=K=8192), from the ncu capture summarised in
-# profiles/gemm_tn_kernel_256x512_bf16_8192cubed_ncu_full.md (mean of two launches).
+# DRAM traffic of one launch of the N=1 workload (M=N=K=8192): dram__bytes_read.sum +
+# dram__bytes_write.sum from an ncu capture of this kernel on this workload, mean of two launches.
 NCU_DRAM_BYTES_PER_LAUNCH_8192 = 985_000_000
 
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
@@ -138,7 +138,7 @@ class ClockSampler:
 
 # ------------------------------------------------------------- GPU helpers ---
 def device_inputs(M, N, K, seed, dtype, device, a_std=None, b_std=None):
-    """Seeded operands of the BASELINE distributions, drawn on the device (statistically the
+    """Seeded operands of the benchmark distributions, drawn on the device (statistically the
     same as the CPU generator the parity tests use; bench inputs are not compared bitwise)."""
     g = torch.Generator(device=device).manual_seed(seed)
     sa = (1.0 / K ** 0.5) if a_std is None else a_std
@@ -169,7 +169,7 @@ def flush_l2(buf):
 
 
 def secondary_shapes(gk, peaks, device):
-    """Other BASELINE shapes, reported beside the headline.  Tensor-bound shapes: L2 flushed
+    """Other benchmark shapes, reported beside the headline.  Tensor-bound shapes: L2 flushed
     between iterations by writing a 512 MiB buffer (several of them fit in the 126 MB L2).
     HBM-bound small-M shapes: timed back to back with no flush, because their streamed operand
     (B, 470 MB) is larger than L2 by itself and a flush would leave 126 MB of dirty lines whose
@@ -476,7 +476,7 @@ def main():
     ap.add_argument("--panels", type=int, default=8)
     ap.add_argument("--nsplit", default="auto", choices=["auto", "fused", "nccl"],
                     help="multi-GPU exchange of C: fused into the GEMM epilogue (default) or NCCL all-gather")
-    ap.add_argument("--no-shapes", action="store_true", help="skip the secondary BASELINE shapes")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the secondary benchmark shapes")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -131,11 +131,13 @@ def gemm_tn_nsplit(A: torch.Tensor, B_shard: torch.Tensor, C: torch.Tensor,
 
 def fanout_pointers(buffer_ptrs, rank: int, column_offset: int, element_size: int) -> list:
     """Device addresses rank `rank` stores its column slab to: the same column offset inside every
-    GPU's C, its own copy first (the local store does not wait behind the link)."""
+    GPU's C.  Its own copy comes first (the local store does not wait behind the link), then the
+    peers in ring order rank+1, rank+2, ...: at any moment the ranks then aim at different
+    destination GPUs instead of all writing to GPU 0, then GPU 1, and so on."""
     world = len(buffer_ptrs)
     if not 0 <= rank < world:
         raise ValueError(f"bad rank {rank} for {world} buffers")
-    order = [rank] + [r for r in range(world) if r != rank]
+    order = [(rank + i) % world for i in range(world)]
     return [int(buffer_ptrs[r]) + column_offset * element_size for r in order]
 
 

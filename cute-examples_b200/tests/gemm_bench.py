@@ -26,7 +26,7 @@ B200_HBM_GBS = 8000.0
 
 REFERENCE_SHAPES = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 16384),
                     (8192, 8192, 8192), (16384, 16384, 4096)]        # (M=N, K) list of gemm_bench.py:616-623
-BASELINE_SHAPES = [(8192, 14336, 4096), (8192, 4096, 14336), (16, 28672, 8192), (64, 28672, 8192),
+TARGET_SHAPES = [(8192, 14336, 4096), (8192, 4096, 14336), (16, 28672, 8192), (64, 28672, 8192),
                    (128, 28672, 8192)]
 
 
@@ -86,7 +86,7 @@ def main():
     name, peak = peak_for_device()
     print(f"device: {torch.cuda.get_device_name()}  SMs: {gk.num_sms()}  nominal dense peak: {peak} TFLOP/s ({name})")
     scratch = torch.zeros(512 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda")
-    shapes = REFERENCE_SHAPES + BASELINE_SHAPES
+    shapes = REFERENCE_SHAPES + TARGET_SHAPES
     if args.quick:
         shapes = [s for s in shapes if 2.0 * s[0] * s[1] * s[2] < 2.5e12]
     print(f"{'M':>6} {'N':>6} {'K':>6} | {'ours ms':>9} {'TFLOP/s':>8} {'GB/s':>8} | {'torch ms':>9} {'TFLOP/s':>8} | speed-up")

@@ -1,7 +1,7 @@
 """Generates tests/golden/gemm_tn_golden.npz from the REFERENCE's own check.
 
 Run in the build container, where the reference tree is mounted:
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of the reference>
 The fixtures travel with the repo; nothing under tests/ reads the reference tree at run time.
 
 What is taken from the reference (kernels/tests/gemm_test.py):
@@ -22,6 +22,7 @@ from __future__ import annotations
 import argparse
 import contextlib
 import hashlib
+import os
 import importlib.util
 import io
 import sys
@@ -67,7 +68,8 @@ def digest(t: torch.Tensor) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT"), required="REFERENCE_ROOT" not in os.environ,
+                    help="root of the reference checkout (or set REFERENCE_ROOT)")
     ap.add_argument("--out", default=str(Path(__file__).resolve().parent / "gemm_tn_golden.npz"))
     args = ap.parse_args()
     measure_error_stats = load_reference_check(Path(args.reference))
@@ -88,7 +90,7 @@ def main() -> None:
         out[f"{name}/meta"] = np.array([M, N, K, seed, oracle.DTYPE_CODE[dtype], int(kind == "ternary")], dtype=np.int64)
         out[f"{name}/ideal_err"] = np.array([max_err, avg_err], dtype=np.float64)
 
-    # BASELINE config 1: 1024^3, seed 0, bf16.  Sampled rows of the ground truth + operand digests.
+    # Benchmark configuration 1: 1024^3, seed 0, bf16.  Sampled rows of the ground truth + operand digests.
     A, B = oracle.make_inputs(1024, 1024, 1024, 0, torch.bfloat16)
     C_ref = torch.matmul(A.float(), B.float().T)
     with contextlib.redirect_stdout(io.StringIO()):

@@ -77,7 +77,7 @@ def test_golden_cases(capi, golden, name, config):
 
 
 def test_config1_1024_cubed(capi, gk, golden):
-    """BASELINE config 1: M=N=K=1024, seed 0, bf16; whole matrix against both oracles, sampled
+    """Benchmark configuration 1: M=N=K=1024, seed 0, bf16; whole matrix against both oracles, sampled
     rows against the fixture, through both call paths."""
     A, B = oracle.make_inputs(1024, 1024, 1024, 0, torch.bfloat16)
     C_ref = oracle.reference_matmul_fp32(A, B)
@@ -292,7 +292,7 @@ def test_split_k_matches_oracle(capi, shape, config):
 
 def test_split_k_automatic_choice(capi):
     """Chosen by itself only when whole tiles would leave more than half of the SMs idle and K is
-    long; never for the BASELINE shapes (measured slower there)."""
+    long; never for the benchmark shapes (measured slower there)."""
     assert capi.gemm_sm100_workspace_bytes(256, 512, 65536, 0) > 0
     for shape in [(4096, 4096, 4096), (8192, 8192, 8192), (128, 28672, 8192), (1024, 1024, 1024)]:
         assert capi.gemm_sm100_workspace_bytes(*shape, 0) == 0
@@ -415,7 +415,7 @@ def test_runs_on_a_side_stream(gk):
     assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
 
 
-# ------------------------------------------------ BASELINE configs 2-4 (1 GPU)
+# ------------------------------------------------ benchmark configurations 2-4 (1 GPU)
 def sampled_check(gk, M, N, K, seed, dtype, a_std, b_std, n_rows=192):
     """Full-size run; the CPU oracle is evaluated on a random sample of rows of A (complete
     rows of C), which pins every column tile and K-block at these sizes."""
@@ -451,8 +451,37 @@ def test_config4_skinny(gk, M):
     sampled_check(gk, M, 28672, 8192, 3, torch.bfloat16, 1.0, 0.02)
 
 
+def test_config5_32768_cubed_sampled_rows(gk):
+    """Benchmark configuration 5 on one GPU: M=N=K=32768, bf16, operands ~N(0,1)/sqrt(K), seed 4
+    (drawn on the device, 2 GiB each, then read back so the CPU oracle sees the same bits).  The
+    oracle is evaluated on 48 sampled rows of A (complete rows of C: every column tile and all
+    512 K blocks), and a second launch must reproduce the first bit for bit."""
+    n = 32768
+    g = torch.Generator(device="cuda").manual_seed(4)
+    A = torch.empty((n, n), dtype=torch.bfloat16, device="cuda")
+    B = torch.empty((n, n), dtype=torch.bfloat16, device="cuda")
+    for t in (A, B):
+        for r0 in range(0, n, 4096):      # fp32 draws in slabs: 0.5 GiB of scratch at a time
+            t[r0:r0 + 4096] = (torch.randn((4096, n), generator=g, device="cuda") / n ** 0.5).to(torch.bfloat16)
+    C = torch.full((n, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A, B, C)
+    gk.device_status()
+    rows = torch.cat([torch.tensor([0, 255, 256, n - 1]), torch.randperm(n, generator=torch.Generator().manual_seed(5))[:44]])
+    rows = torch.unique(rows)
+    got = C[rows.cuda()].cpu()
+    assert not torch.isnan(got.float()).any()
+    C_ref = oracle.reference_matmul_fp32(A[rows.cuda()].cpu(), B.cpu())
+    err = oracle.normalized_max_error(got, C_ref)
+    assert err <= oracle.tolerance(torch.bfloat16), f"normalised max error {err:.3e}"
+    checksum = C.view(torch.int16).to(torch.int32).sum(dtype=torch.int64).item()
+    C.fill_(float("nan"))
+    gk.gemm_tn_test(A, B, C)
+    gk.device_status()
+    assert C.view(torch.int16).to(torch.int32).sum(dtype=torch.int64).item() == checksum
+
+
 def test_full_size_identity_property(gk):
-    """Size-independent property at a full BASELINE size: with B = I (8192 x 8192) the output
+    """Size-independent property at a full benchmark size: with B = I (8192 x 8192) the output
     must reproduce A bit for bit."""
     n = 8192
     g = torch.Generator(device="cuda").manual_seed(7)
