@@ -5,26 +5,34 @@
 // It replaces the reference's Hopper kernel test::gemm_kernel
 // (kernels/gemm_kernels/sm90a/gemm.cuh:246-418, 452-462): same math and the same
 // "both operands K-major" layout contract, but none of its structure.  Roles per CTA
-// (192 threads):
-//   warp 0      TMA producer   : global -> smem ring of kStages (A tile + B tile), mbarrier tx-count
-//   warp 1      MMA issuer     : one thread issues tcgen05.mma from smem descriptors into TMEM;
-//                                 tcgen05.commit frees ring slots and publishes finished accumulators
+// (64 + 32 x kEpiWarps threads):
+//   warp 0      TMA producer   : global -> smem ring of kStages (A tile + B tile(s)), mbarrier tx-count
+//   warp 1      MMA issuer     : tcgen05.mma from smem descriptors into TMEM; tcgen05.commit frees
+//                                 ring slots and publishes finished accumulators
 //   warps 2..   epilogue       : tcgen05.ld TMEM -> registers -> 16-bit -> swizzled smem -> TMA store
+// Warps 0 and 1 run their loops with all 32 lanes and warp-uniform waits; one elected lane
+// issues.  (TMA and MMA instructions take uniform-register operands: a loop run by a single
+// diverged lane pays a register move per operand and was measured at 0.74 of the tensor rate.)
+//
 // Two accumulator slots live in TMEM (2 x kMmaN fp32 columns).  Either consecutive tiles
 // alternate between them, so the epilogue of tile i runs under the mainloop of tile i+1
 // (the reference's single register-resident accumulator idles the tensor pipe during every
 // epilogue, gemm.cuh:368-395), or one double-width tile owns both (see GemmConfig).
 //
 // kCtaGroup == 2 pairs two CTAs (a 2-CTA cluster) on one 256 x kBlockN tile: each CTA
-// loads its own 128 rows of A and its own kBlockN/2 rows of B with plain TMA loads, and
+// loads its own 128 rows of A and its own share of the B rows with plain TMA loads, and
 // the leader CTA issues cta_group::2 MMAs that read both CTAs' shared memory.  This gives
 // the operand sharing that the reference gets from a cluster-broadcast load of B
 // (gemm_test.cu:60-64) without any broadcast load.
 //
-// Every wait on an mbarrier is bounded: when a wait runs out the CTA (and its pair
-// peer) is flagged, all roles fall through to the common tear-down, TMEM is released and
-// the launcher reports the status word.  The reference's waits are unbounded
-// (gemm.cuh:75-78, 91-94).
+// Work is handed out as segments (WorkIter): whole tiles in a static persistent order, or, for
+// the K-split schedule, equal runs of K blocks with fp32 partial tiles for the tiles a run
+// boundary cuts.  The finished tile can be stored through several output tensor maps
+// (gemm_tn_fanout_kernel): that is how the column-sharded multi-GPU GEMM writes every GPU's C.
+//
+// Every wait is bounded: when one runs out the CTA (and its pair peer) is flagged, all roles
+// fall through to the common tear-down, TMEM is released and the launcher reports the status
+// word.  The reference's waits are unbounded (gemm.cuh:75-78, 91-94).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
