@@ -413,6 +413,16 @@ def run_multi(args):
     ms = t.item() / args.steps
     tflops = gemm_flops(M, N, K) / ms / 1e9
 
+    # this rank's GEMM alone (no exchange), same number of steps: shows what the exchange costs
+    C_slab = torch.empty((M, hi - lo), dtype=dtype, device=device)
+    local_step = lambda: gk.gemm_tn_test(A, B_shard, C_slab)  # noqa: E731
+    local_step()
+    local_total = time_steps(local_step, args.steps, torch.cuda.synchronize, barrier)
+    t = torch.tensor([local_total], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    local_ms = t.item() / args.steps
+    del C_slab
+
     # end to end: operands start in pinned host memory, the result ends there, every step.  The
     # host holds ONE copy of A, B and C between the ranks: rank g uploads its 1/G of A's rows and
     # its shard of B, the ranks replicate A over NVLink (NCCL all-gather, far faster than G
@@ -448,6 +458,8 @@ def run_multi(args):
             "config": {"workload": f"cfg5 bf16 TN GEMM M=N=K=32768, B row-sharded over {world} GPUs, {how}",
                        "M": M, "N": N, "K": K, "nsplit_mode": mode,
                        "per_gpu_tflops": round(per_gpu, 2),
+                       "local_gemm_ms_per_step": round(local_ms, 4),
+                       "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange",
                        "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"},
             "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,

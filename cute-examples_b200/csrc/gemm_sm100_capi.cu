@@ -343,7 +343,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   attrs[0].val.clusterDim.y = 1;
   attrs[0].val.clusterDim.z = 1;
   cfg.attrs = attrs;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = Cfg::kCtaGroup == 2 ? 1 : 0;          // single-CTA tiles are launched without a cluster
   e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
