@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/gemm_sm100.h"
@@ -61,15 +62,38 @@ struct DeviceState {
 
 std::mutex g_mutex;
 DeviceState g_dev[kMaxDevices];
-long g_opt_tile_config = -1;
-long g_opt_timeout_ms = 2000;
-long g_opt_max_ctas = 0;
-long g_opt_debug_flags = 0;
-long g_opt_group_m = 0;
-long g_opt_k_rotate = 0;      // 0 never (default: measured no gain on B200), 1 always, -1 when there is a single tile row
-long g_opt_split_k = -1;     // -1 automatic, 0 never, 1 whenever the configuration allows it
-unsigned long long* g_trace_ptr = nullptr;   // device buffer for per-CTA trace records, or null
-size_t g_trace_bytes = 0;
+// Process-wide knobs.  Written by gemm_sm100_set_option / gemm_sm100_set_trace_buffer, read by
+// launches on any thread: atomics, so a concurrent change is seen whole or not at all.
+std::atomic<long> g_opt_tile_config{-1};
+std::atomic<long> g_opt_timeout_ms{2000};
+std::atomic<long> g_opt_max_ctas{0};
+std::atomic<long> g_opt_debug_flags{0};
+std::atomic<long> g_opt_group_m{0};
+std::atomic<long> g_opt_k_rotate{0};    // 0 never (default: measured no gain on B200), 1 always, -1 when there is a single tile row
+std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
+std::atomic<unsigned long long*> g_trace_ptr{nullptr};   // device buffer for per-CTA trace records, or null
+std::atomic<size_t> g_trace_bytes{0};
+
+// Optional overrides from the environment, read once when the library is loaded:
+// GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M, GEMM_SM100_MAX_CTAS,
+// GEMM_SM100_TIMEOUT_MS (same meaning and ranges as gemm_sm100_set_option; bad values are ignored).
+struct EnvOverrides {
+  static void read(const char* name, std::atomic<long>& target, long lo, long hi) {
+    const char* text = std::getenv(name);
+    if (!text || !*text) return;
+    char* end = nullptr;
+    const long v = std::strtol(text, &end, 10);
+    if (end && *end == '\0' && v >= lo && v <= hi) target = v;
+  }
+  EnvOverrides() {
+    read("GEMM_SM100_TILE_CONFIG", g_opt_tile_config, -1, kNumConfigs - 1);
+    read("GEMM_SM100_SPLIT_K", g_opt_split_k, -1, 1);
+    read("GEMM_SM100_GROUP_M", g_opt_group_m, 0, 4096);
+    read("GEMM_SM100_MAX_CTAS", g_opt_max_ctas, 0, 1 << 20);
+    read("GEMM_SM100_TIMEOUT_MS", g_opt_timeout_ms, 1, 60000);
+  }
+};
+const EnvOverrides g_env_overrides;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -242,7 +266,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
   using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
   // The instrumented instantiation runs only while a trace buffer or an experiment flag is set.
-  const bool debug = g_trace_ptr != nullptr || g_opt_debug_flags != 0;
+  const bool debug = g_trace_ptr.load() != nullptr || g_opt_debug_flags.load() != 0;
   auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
   if constexpr (has_split_k(kCfgIndex)) {
     if (plan.split_k) kernel = gemm_tn_kernel<Cfg, false, true>;
@@ -296,11 +320,11 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
   // Rasterisation group: 16 tile rows when the problem has that many (measured best from 8192
   // to 32768 rows: the A panel of a group is reused by more B tiles), else 8.
-  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : (tp.m_tiles >= 16 ? 16 : 8);
+  tp.group_m = g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (tp.m_tiles >= 16 ? 16 : 8);
   tp.status = st.status_ptr;
-  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
+  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
   tp.trace = nullptr;
-  tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags);
+  tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
   tp.sk_flags = nullptr;
   tp.sk_partials = nullptr;
   tp.sk_rows = 128;
@@ -329,8 +353,9 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
     ctas = st.max_ctas[kCfgIndex][dt];
   }
 
-  if (g_trace_ptr && g_trace_bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
-    tp.trace = g_trace_ptr;
+  unsigned long long* const trace_ptr = g_trace_ptr.load();
+  if (trace_ptr && g_trace_bytes.load() >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
+    tp.trace = trace_ptr;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
@@ -373,9 +398,9 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
   tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
   tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
   tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
-  tp.group_m = g_opt_group_m > 0 ? static_cast<int>(g_opt_group_m) : (tp.m_tiles >= 16 ? 16 : 8);
+  tp.group_m = g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (tp.m_tiles >= 16 ? 16 : 8);
   tp.status = st.status_ptr;
-  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull;
+  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
   tp.trace = nullptr;
   tp.debug_flags = 0;
   tp.sk_flags = nullptr;
@@ -571,7 +596,7 @@ int gemm_sm100_selftest_wait_timeout(void* cuda_stream, int* cuda_error_out) {
     if (rc != GEMM_SM100_OK) return rc;
   }
   wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      st->status_ptr, static_cast<unsigned long long>(g_opt_timeout_ms) * 1000000ull);
+      st->status_ptr, static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? GEMM_SM100_OK : set_cuda_error(cuda_error_out, e);
 }

@@ -712,6 +712,12 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   }
 
   // ------------------------------------------------------------------ tear-down
+  if (*abort_flag != 0) {
+    // A wait gave up: loads this CTA issued may still be in flight towards its shared memory.
+    // Give them time to land (they take microseconds) before the memory is handed back.
+#pragma unroll 1
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
   tc_fence_before_sync();
   __syncthreads();
   if constexpr (G == 2) {

@@ -121,7 +121,9 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  * "split_k" (-1 = automatic, 0 = never, 1 = whenever the chosen configuration has a K-split
  * variant), "group_m" (0 = default; tile rows per rasterisation group), "k_rotate" (0 = off, the default; 1 = on; -1 = on for a single tile row:
  * start each tile's K loop at a different K block).  Set them before
- * asking gemm_sm100_workspace_bytes, which depends on them.
+ * asking gemm_sm100_workspace_bytes, which depends on them.  The environment variables
+ * GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M, GEMM_SM100_MAX_CTAS and
+ * GEMM_SM100_TIMEOUT_MS give the initial values when the library is loaded.
  * The reference's equivalents are compile-time constants (gemm.cuh:420-451). */
 int gemm_sm100_set_option(const char* name, long value);
 

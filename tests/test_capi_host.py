@@ -106,3 +106,22 @@ def test_binding_rejects_bad_tensors_with_runtime_error():
     # keyword names of the reference binding
     with pytest.raises(RuntimeError):
         gk.gemm_tn_test(A=z(8, 8), B=z(8, 8), C=z(8, 8))
+
+
+def test_environment_overrides_are_read_at_load():
+    """A fresh process that sets GEMM_SM100_TILE_CONFIG sees it as the initial option value:
+    select_config then returns that configuration whatever the shape."""
+    import os
+    import subprocess
+    import sys
+
+    code = ("import ctypes;"
+            f"lib = ctypes.CDLL({str(LIB_PATH)!r});"
+            "lib.gemm_sm100_select_config.argtypes = [ctypes.c_int] * 4;"
+            "print(lib.gemm_sm100_select_config(8192, 8192, 8192, 0), lib.gemm_sm100_select_config(128, 256, 64, 0))")
+    env = dict(os.environ, GEMM_SM100_TILE_CONFIG="2")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, check=True).stdout.split()
+    assert out == ["2", "2"]
+    env = dict(os.environ, GEMM_SM100_TILE_CONFIG="99")           # out of range: ignored
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, check=True).stdout.split()
+    assert out[0] == "1"
