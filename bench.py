@@ -295,10 +295,10 @@ def run_single(args):
     gk.device_status()
     ms = ms_total / args.steps
     tflops = gemm_flops(M, N, K) / ms / 1e9
-    # the clock the kernel really runs at under this load (right after the timed region, GPU warm)
-    for _ in range(3):
-        step()
-    sm_mhz_in_kernel = gk.measure_sm_clock_mhz(A, B, C)
+    # SM cycles one launch needs (from the per-CTA trace counters; independent of the clock):
+    # cycles / measured time per step = the clock the timed region really ran at
+    traced = gk.trace_launch(A, B, C)
+    sm_mhz_effective = traced["cycles"] / (ms * 1e3)
 
     # end to end through the public host-memory entry point: pinned host operands in, host result
     # out, every step (uploads of A panels, GEMM panels and downloads of C panels overlap)
@@ -338,10 +338,11 @@ def run_single(args):
                 "api": "gemm_kernels.HostGemm (A uploaded in row panels; GEMM and download of C per panel)",
                 "max_abs_diff_vs_device_path": e2e_check},
         "gpu_launches": args.steps,
-        "clocks": dict(clk.summary(), sm_mhz_in_kernel=round(sm_mhz_in_kernel, 0),
-                       note="sm_mhz / reasons: NVML samples during the timed region; sm_mhz_in_kernel: "
-                            "clock64 over %globaltimer inside one traced launch right after it, i.e. with "
-                            "the power cap at its tightest (the kernel needs ~931k cycles at any clock)"),
+        "clocks": dict(clk.summary(), kernel_cycles=round(traced["cycles"]),
+                       sm_mhz_effective=round(sm_mhz_effective),
+                       note="sm_mhz / reasons: NVML samples during the timed region (NVML does not follow the "
+                            "fast power-cap steps); kernel_cycles: SM cycles of one launch from the kernel's "
+                            "trace counters; sm_mhz_effective = kernel_cycles / ms_per_step"),
         "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(tflops / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH_8192,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this "
@@ -506,7 +507,7 @@ def main():
         args.warmup = 3 if args.warmup is None else args.warmup
         run_multi(args)
     else:
-        args.steps = args.steps or 200
+        args.steps = args.steps or 50
         args.warmup = 5 if args.warmup is None else args.warmup
         run_single(args)
 

@@ -42,11 +42,12 @@ LIBRARY_PATH = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "libg
 DTYPE_CODES = {_torch.bfloat16: 0, _torch.float16: 1}
 
 
-def measure_sm_clock_mhz(A: "_torch.Tensor", B: "_torch.Tensor", C: "_torch.Tensor") -> float:
-    """SM clock in MHz during one traced launch of ``gemm_tn_test(A, B, C)``: cycles (clock64)
-    over nanoseconds (%globaltimer) between kernel entry and exit, averaged over the CTAs.  This is
-    the clock the kernel really ran at; the driver-reported clock does not follow the fast
-    power-management steps of a power-capped GPU."""
+def trace_launch(A: "_torch.Tensor", B: "_torch.Tensor", C: "_torch.Tensor") -> dict:
+    """Runs ``gemm_tn_test(A, B, C)`` once with the per-CTA trace counters on and returns
+    ``{"cycles": mean SM cycles from kernel entry to exit, "ns": mean wall time of a CTA,
+    "sm_mhz": cycles / ns * 1000}``.  The cycle count does not depend on the clock, so
+    ``cycles / (measured seconds per launch)`` gives the clock a timed run really had; the
+    driver-reported clock does not follow the fast power-management steps of a power-capped GPU."""
     trace = _torch.zeros(num_sms() * 16, dtype=_torch.int64, device=A.device)
     set_trace_buffer(trace)
     try:
@@ -57,10 +58,11 @@ def measure_sm_clock_mhz(A: "_torch.Tensor", B: "_torch.Tensor", C: "_torch.Tens
     t = trace.view(-1, 16).cpu()
     used = t[:, 13] > t[:, 12]
     if not bool(used.any()):
-        return float("nan")
+        return {"cycles": float("nan"), "ns": float("nan"), "sm_mhz": float("nan")}
     cycles = (t[used, 10] - t[used, 0]).double()
     ns = (t[used, 13] - t[used, 12]).double()
-    return float((cycles / ns).mean().item() * 1000.0)
+    return {"cycles": float(cycles.mean().item()), "ns": float(ns.mean().item()),
+            "sm_mhz": float((cycles / ns).mean().item() * 1000.0)}
 
 
 def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" = None) -> "_torch.Tensor":
@@ -123,5 +125,5 @@ from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, sh
 
 __all__ = [
     "gemm_tn_test", "gemm_tn", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
-    "set_option", "set_trace_buffer", "measure_sm_clock_mhz", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
+    "set_option", "set_trace_buffer", "trace_launch", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]
