@@ -168,7 +168,14 @@ def flush_l2(buf):
     buf.add_(1)
 
 
-def secondary_shapes(gk, peaks, device):
+def cpu_rows_for(M, N, K, target_flops=6.0e10):
+    """Rows of A for the CPU leg of a shape: the whole problem when it is small, else a slab worth
+    about `target_flops` (a fraction of a second on a server CPU)."""
+    rows = int(max(64, min(M, target_flops / (2.0 * N * K))))
+    return M if rows >= M else max(64, rows // 64 * 64)
+
+
+def secondary_shapes(gk, peaks, device, with_cpu=True):
     """Other benchmark shapes, reported beside the headline.  Tensor-bound shapes: L2 flushed
     between iterations by writing a 512 MiB buffer (several of them fit in the 126 MB L2).
     HBM-bound small-M shapes: timed back to back with no flush, because their streamed operand
@@ -221,6 +228,18 @@ def secondary_shapes(gk, peaks, device):
             rec["frac"] = round(tf / peaks["bf16_tflops"], 4)
         else:
             rec["frac"] = round(gbs / peaks["hbm_gbs"], 4)
+        if with_cpu:
+            # the same operands on the host cores: the reference's check expression, fp32
+            from oracle import oracle
+
+            rows = cpu_rows_for(M, N, K)
+            Ac, Bc = A[:rows].cpu(), B.cpu()
+            sec, threads, C_ref = oracle.time_cpu_matmul(Ac, Bc, min_seconds=0.0, max_runs=1)
+            rec["cpu_tflops"] = round(gemm_flops(rows, N, K) / sec / 1e12, 3)
+            rec["cpu_cores"] = threads
+            rec["cpu_rows"] = rows
+            rec["norm_max_err"] = float(f"{oracle.normalized_max_error(C[:rows].cpu(), C_ref):.3e}")
+            del Ac, Bc, C_ref
         out.append(rec)
         del A, B, C
     gk.device_status()
@@ -319,7 +338,7 @@ def run_single(args):
     e2e_check = float((Ch[::1024].float() - C[::1024].cpu().float()).abs().max().item())
     del host_gemm
 
-    shapes = [] if args.no_shapes else secondary_shapes(gk, peaks, device)
+    shapes = [] if args.no_shapes else secondary_shapes(gk, peaks, device, with_cpu=not args.no_cpu)
     cpu = None if args.no_cpu else cpu_baseline_sample(M, N, K, 1, rows=2048)
 
     timed_s = ms_total / 1e3
