@@ -260,6 +260,31 @@ Plan make_plan(int M, int N, int K, int sm_count) {
   return best;
 }
 
+// Tile counts, rasterisation and wait limit of one launch (everything that does not depend on
+// the schedule variant).
+template <class Cfg>
+TileParams base_tile_params(const Problem& p, const DeviceState& st) {
+  TileParams tp;
+  tp.M = p.M;
+  tp.N = p.N;
+  tp.K = p.K;
+  tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
+  tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
+  tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
+  // Rasterisation group: 16 tile rows when the problem has that many (measured best from 8192
+  // to 32768 rows: the A panel of a group is reused by more B tiles), else 8.
+  tp.group_m = g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (tp.m_tiles >= 16 ? 16 : 8);
+  tp.status = st.status_ptr;
+  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
+  tp.trace = nullptr;
+  tp.debug_flags = 0;
+  tp.sk_flags = nullptr;
+  tp.sk_partials = nullptr;
+  tp.sk_rows = 128;
+  tp.k_rotate = 0;
+  return tp;
+}
+
 template <int kCfgIndex, bool kIsBf16>
 int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceState& st, cudaStream_t stream,
                   int* cuda_error_out) {
@@ -311,23 +336,8 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
     }
   }
 
-  TileParams tp;
-  tp.M = p.M;
-  tp.N = p.N;
-  tp.K = p.K;
-  tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
-  tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
-  tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
-  // Rasterisation group: 16 tile rows when the problem has that many (measured best from 8192
-  // to 32768 rows: the A panel of a group is reused by more B tiles), else 8.
-  tp.group_m = g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (tp.m_tiles >= 16 ? 16 : 8);
-  tp.status = st.status_ptr;
-  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
-  tp.trace = nullptr;
+  TileParams tp = base_tile_params<Cfg>(p, st);
   tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
-  tp.sk_flags = nullptr;
-  tp.sk_partials = nullptr;
-  tp.sk_rows = 128;
   tp.k_rotate = (g_opt_k_rotate > 0 || (g_opt_k_rotate < 0 && tp.m_tiles == 1 && !plan.split_k)) ? 1 : 0;
   if (plan.split_k) {
     tp.sk_flags = static_cast<unsigned int*>(workspace);
@@ -391,22 +401,7 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
       st.fanout_attr_set[kCfgIndex][dt] = true;
     }
   }
-  TileParams tp;
-  tp.M = p.M;
-  tp.N = p.N;
-  tp.K = p.K;
-  tp.m_tiles = static_cast<int>(ceil_div(p.M, 128L * Cfg::kCtaGroup));
-  tp.n_tiles = static_cast<int>(ceil_div(p.N, Cfg::kBlockN));
-  tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
-  tp.group_m = g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (tp.m_tiles >= 16 ? 16 : 8);
-  tp.status = st.status_ptr;
-  tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
-  tp.trace = nullptr;
-  tp.debug_flags = 0;
-  tp.sk_flags = nullptr;
-  tp.sk_partials = nullptr;
-  tp.sk_rows = 128;
-  tp.k_rotate = 0;
+  const TileParams tp = base_tile_params<Cfg>(p, st);
 
   CUtensorMap map_a, map_b;
   OutputMaps out;

@@ -310,12 +310,12 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   const uint32_t smem_b = base + kStages * Cfg::kABytes;
   const uint32_t smem_epi = smem_b + kStages * Cfg::kBBytes;
   uint8_t* bar_mem = smem + kStages * Cfg::kStageBytes + Cfg::kEpiBytes;
-  // barrier block: full[kStages], empty[kStages], tfull[2], tempty[2], then two words
+  // barrier block: full[kStages], empty[kStages], tfull[2], tempty[2], tmem_ready, then two words
   const uint32_t bar_base = smem_u32(bar_mem);
   constexpr uint32_t kFullOff = 0, kEmptyOff = 8u * kStages, kTFullOff = 16u * kStages,
-                     kTEmptyOff = 16u * kStages + 16u;
-  static_assert(8 * (2 * kStages + 4) + 8 <= Cfg::kBarrierBytes, "barrier block too small");
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kStages + 4));
+                     kTEmptyOff = 16u * kStages + 16u, kTmemReadyOff = 16u * kStages + 32u;
+  static_assert(8 * (2 * kStages + 5) + 8 <= Cfg::kBarrierBytes, "barrier block too small");
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kStages + 5));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -343,22 +343,34 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       mbar_init(bar_base + kTFullOff + 8u * a, 1);                     // one tcgen05.commit per use
       mbar_init(bar_base + kTEmptyOff + 8u * a, Cfg::kEpiWarps * G);   // every epilogue warp of the pair arrives once
     }
+    mbar_init(bar_base + kTmemReadyOff, 1);   // pair mode: the peer's TMEM allocation is done
     fence_mbar_init();
   }
-  if (warp == 1) {
-    tmem_alloc<G>(smem_u32(tmem_slot), Cfg::kTmemCols);
-    tmem_relinquish<G>();
-  }
-  tc_fence_before_sync();
+  // Barriers are initialised: let the producer go.  The TMEM allocation (slow for a CTA pair)
+  // happens after this point, off the path of the first operand loads.
   __syncthreads();
   if constexpr (G == 2) {
     cluster_arrive();
     cluster_wait();
   }
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
   if constexpr (kDebug)
     if (trace && threadIdx.x == 0) trace[kTraceSetupDone] = clock64();
+  uint32_t tmem_base = 0;
+  if (warp >= 1) {
+    // TMEM address hand-over between the allocating warp and the epilogue warps only.
+    if (warp == 1) {
+      tmem_alloc<G>(smem_u32(tmem_slot), Cfg::kTmemCols);
+      tmem_relinquish<G>();
+      tc_fence_before_sync();
+    }
+    named_barrier_sync(1, Cfg::kThreads - 32);
+    tc_fence_after_sync();
+    tmem_base = *tmem_slot;
+    if constexpr (G == 2) {
+      // The leader's MMAs write both CTAs' TMEM: it must know the peer's allocation is done.
+      if (warp == 1 && !is_leader && lane == 0) mbar_arrive_cluster(map_to_cta(bar_base + kTmemReadyOff, 0u));
+    }
+  }
 
   const int num_tiles = p.m_tiles * p.n_tiles;
   const int cluster_id = blockIdx.x / G;
@@ -437,6 +449,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     // descriptors plus a constant.
     if (is_leader) {
       const bool issuer = elect_one();
+      bool peer_ready = true;
+      if constexpr (G == 2) peer_ready = wait_bounded(bar_base + kTmemReadyOff, 0u, ctx, kStatusTimeoutMmaAcc + 0xf);
       constexpr uint32_t idesc = make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN);
       const uint64_t da0 = make_smem_desc_sw128(smem_a);
       const uint64_t db0 = make_smem_desc_sw128(smem_b);
@@ -446,7 +460,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       Segment seg;
       bool have = work.next(seg);
       int kb = seg.kb0, iter = 0;          // iter counts segments: it selects the accumulator slot
-      bool ok = true;
+      bool ok = peer_ready;
       long long stall_full = 0, stall_acc = 0;
       const bool skip_mma = kDebug && (dbg & kDebugSkipMma);
       while (have && ok) {
