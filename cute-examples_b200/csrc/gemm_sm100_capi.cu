@@ -58,6 +58,7 @@ struct DeviceState {
   int max_ctas[kNumConfigs][2] = {};   // persistent grid limit per config and dtype
   bool attr_set[kNumConfigs][2] = {};
   bool fanout_attr_set[2][2] = {};
+  bool nn_attr_set[4][2] = {};
 };
 
 std::mutex g_mutex;
@@ -167,6 +168,7 @@ struct Problem {
   int M, N, K;
   long lda, ldb, ldc;
   int dtype;
+  bool b_is_kn = false;   // B given as [K, N] (pitch ldb >= N) instead of [N, K]
 };
 
 int validate(const Problem& p) {
@@ -175,7 +177,7 @@ int validate(const Problem& p) {
   if (p.M == 0 || p.N == 0) return GEMM_SM100_OK;
   if (!p.C || (p.K > 0 && (!p.A || !p.B))) return GEMM_SM100_ERR_NULL_POINTER;
   if (p.K % 8 != 0) return GEMM_SM100_ERR_BAD_SHAPE;
-  if (p.lda < p.K || p.ldb < p.K || p.ldc < p.N) return GEMM_SM100_ERR_BAD_SHAPE;
+  if (p.lda < p.K || p.ldb < (p.b_is_kn ? p.N : p.K) || p.ldc < p.N) return GEMM_SM100_ERR_BAD_SHAPE;
   if (p.lda % 8 != 0 || p.ldb % 8 != 0 || p.ldc % 8 != 0) return GEMM_SM100_ERR_BAD_ALIGNMENT;
   if ((reinterpret_cast<uintptr_t>(p.A) | reinterpret_cast<uintptr_t>(p.B) |
        reinterpret_cast<uintptr_t>(p.C)) & 15u)
@@ -213,7 +215,7 @@ inline int grid_cap(const ConfigInfo& c, int sm_count) {
 
 // The K-split schedule gives every CTA the same number of K blocks; it pays when whole tiles
 // quantise badly over the SMs (few tiles, as in the memory-bound small-M shapes) and K is long.
-Plan make_plan(int M, int N, int K, int sm_count) {
+Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true) {
   Plan best;
   double best_cost = 1e300;
   const long k_blocks = ceil_div(K, 64);
@@ -243,7 +245,7 @@ Plan make_plan(int M, int N, int K, int sm_count) {
     // exposed epilogues per CTA pair and the lost lockstep sharing of operands cost more than the
     // idle quarter wave.  So a bad wave count alone does not select it.)
     const bool auto_split = g_opt_split_k < 0 && units >= slots * 16 && tiles * 2 <= slots;
-    const bool can_split = has_split_k(i) && units >= 2;
+    const bool can_split = allow_split && has_split_k(i) && units >= 2;
     if (can_split && (g_opt_split_k > 0 || auto_split)) {
       cost = split_cost;
       cand.split_k = true;
@@ -435,6 +437,58 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
   return GEMM_SM100_OK;
 }
 
+// Launch of the B[K,N] variant (whole tiles only: no K-split, no trace instantiation).
+template <int kCfgIndex, bool kIsBf16>
+int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
+  constexpr ConfigInfo ci = kConfigs[kCfgIndex];
+  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  auto kernel = gemm_nn_kernel<Cfg>;
+  constexpr int dt = kIsBf16 ? 0 : 1;
+  cudaError_t e;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!st.nn_attr_set[kCfgIndex][dt]) {
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      st.nn_attr_set[kCfgIndex][dt] = true;
+    }
+  }
+  const TileParams tp = base_tile_params<Cfg>(p, st);
+  CUtensorMap map_a, map_b, map_c;
+  int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  if (rc) return rc;
+  rc = encode_2d(&map_b, p.B, p.dtype, p.K, p.N, p.ldb, 64, cuda_error_out);     // K rows of N columns
+  if (rc) return rc;
+  rc = encode_2d(&map_c, p.C, p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.ctas));
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = Cfg::kCtaGroup;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = Cfg::kCtaGroup == 2 ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  return GEMM_SM100_OK;
+}
+
+template <bool kIsBf16>
+int dispatch_nn(const Plan& plan, const Problem& p, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
+  switch (plan.config) {
+    case 0: return launch_nn<0, kIsBf16>(p, plan, st, stream, cuda_error_out);
+    case 1: return launch_nn<1, kIsBf16>(p, plan, st, stream, cuda_error_out);
+    case 2: return launch_nn<2, kIsBf16>(p, plan, st, stream, cuda_error_out);
+    case 3: return launch_nn<3, kIsBf16>(p, plan, st, stream, cuda_error_out);
+    default: return GEMM_SM100_ERR_BAD_OPTION;
+  }
+}
+
 template <bool kIsBf16>
 int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
   switch (plan.config) {
@@ -580,6 +634,39 @@ int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int
                 : launch_fanout<0, true>(p, outputs, num_outputs, *st, stream, cuda_error_out);
   return wide ? launch_fanout<1, false>(p, outputs, num_outputs, *st, stream, cuda_error_out)
               : launch_fanout<0, false>(p, outputs, num_outputs, *st, stream, cuda_error_out);
+}
+
+int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                  int dtype, void* cuda_stream, int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype, true};
+  int rc = validate(p);
+  if (rc != GEMM_SM100_OK) return rc;
+  if (M == 0 || N == 0) return GEMM_SM100_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (K == 0) {
+    cudaError_t e = cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 2, 0, static_cast<size_t>(N) * 2,
+                                      static_cast<size_t>(M), stream);
+    return e == cudaSuccess ? GEMM_SM100_OK : set_cuda_error(cuda_error_out, e);
+  }
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    rc = get_encoder(cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+  }
+  Plan plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false);
+  if (plan.config > 3) plan = Plan{};       // the experimental configurations have no B[K,N] variant
+  if (plan.ctas == 0) {
+    const long tiles = ceil_div(M, 256L) * ceil_div(N, 256L);
+    const long slots = st->sm_count / 2;
+    plan.config = 0;
+    plan.ctas = static_cast<int>((tiles < slots ? tiles : slots) * 2);
+  }
+  if (dtype == GEMM_SM100_BF16) return dispatch_nn<true>(plan, p, *st, stream, cuda_error_out);
+  return dispatch_nn<false>(plan, p, *st, stream, cuda_error_out);
 }
 
 int gemm_sm100_selftest_wait_timeout(void* cuda_stream, int* cuda_error_out) {

@@ -285,11 +285,16 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
 // every one of them (one for the plain GEMM; the column-sharded multi-GPU path passes one map
 // per GPU, each describing this rank's column slab inside that GPU's C, so the all-gather of C
 // happens in the epilogue as TMA stores over NVLink).
-template <class Cfg, bool kDebug, bool kSplitK>
+//
+// kBIsKN: B is given as [K, N] (N contiguous, the "NN" product A * B) instead of [N, K].  Only the
+// B loads and the B descriptors change: a stage then holds B as 64-column blocks of 64 K rows
+// (one TMA box each), described to the tensor core as an MN-major operand.
+template <class Cfg, bool kDebug, bool kSplitK, bool kBIsKN = false>
 __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                              const CUtensorMap* tmap_c, const int num_c, const TileParams& p) {
   constexpr int G = Cfg::kCtaGroup;
   constexpr int kStages = Cfg::kStages;
+  static_assert(!kBIsKN || Cfg::kBRows % 64 == 0, "B[K,N] tiles are loaded in blocks of 64 columns");
   unsigned long long* trace = nullptr;
   unsigned int dbg = 0;
   if constexpr (kDebug) {
@@ -423,9 +428,18 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
             tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
 #pragma unroll
-            for (int h = 0; h < Cfg::kHalves; ++h)
-              tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, x,
-                             row_b + h * Cfg::kMmaN, pol);
+            for (int h = 0; h < Cfg::kHalves; ++h) {
+              if constexpr (!kBIsKN) {
+                tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, x,
+                               row_b + h * Cfg::kMmaN, pol);
+              } else {
+                // B[K, N]: coordinates are (column of B, K); one 64 x 64 box per block of 64 columns
+#pragma unroll
+                for (int j = 0; j < Cfg::kBRows / 64; ++j)
+                  tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes + j * 8192, &tmap_b,
+                                 full_leader + 8u * s, row_b + h * Cfg::kMmaN + j * 64, x, pol);
+              }
+            }
           }
           if (++kb == seg.kb1) {
             have = work.next(seg);
@@ -451,9 +465,13 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       const bool issuer = elect_one();
       bool peer_ready = true;
       if constexpr (G == 2) peer_ready = wait_bounded(bar_base + kTmemReadyOff, 0u, ctx, kStatusTimeoutMmaAcc + 0xf);
-      constexpr uint32_t idesc = make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN);
+      constexpr uint32_t idesc =
+          make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN, kBIsKN ? 1u : 0u);
       const uint64_t da0 = make_smem_desc_sw128(smem_a);
-      const uint64_t db0 = make_smem_desc_sw128(smem_b);
+      const uint64_t db0 = kBIsKN ? make_smem_desc_sw128_mn(smem_b, 8192) : make_smem_desc_sw128(smem_b);
+      // start-address step (16-byte units) of B per 16-element K step: 32 bytes along a K-major row,
+      // two 8-row groups of 1024 bytes for the MN-major layout
+      constexpr uint32_t kBStepK = kBIsKN ? 128u : 2u;
       const uint32_t bar_peer = (G == 2) ? map_to_cta(bar_base, 1u) : bar_base;
       uint32_t phase = 0;
       WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
@@ -513,7 +531,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
                 umma_f16<G>(tmem_d, da, db, idesc, first_kb ? 0u : 1u);   // first K step of a segment overwrites
 #pragma unroll
                 for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k)
-                  umma_f16<G>(tmem_d, da + 2u * k, db + 2u * k, idesc, 1u);
+                  umma_f16<G>(tmem_d, da + 2u * k, db + kBStepK * k, idesc, 1u);
               }
               if (last_kb) {                                             // this half's accumulator is complete
                 if (skip_mma) {
@@ -755,6 +773,14 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
   gemm_tn_body<Cfg, kDebug, kSplitK>(tmap_a, tmap_b, &tmap_c, 1, p);
+}
+
+// C = A[M,K] * B[K,N]: same kernel, B loaded and described as an MN-major operand.
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+gemm_nn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
+  gemm_tn_body<Cfg, false, false, true>(tmap_a, tmap_b, &tmap_c, 1, p);
 }
 
 // Self-test of the bounded wait: one warp waits on a barrier that nothing ever arrives on.  The

@@ -312,10 +312,26 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor for kind::f16: fp32 accumulate, A and B both K-major.
-// `ab_format`: 0 = fp16, 1 = bf16.  M and N are the full (pair-wide) MMA extents.
-__host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t ab_format, uint32_t m, uint32_t n) {
-  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// Shared-memory matrix descriptor for an MN-major operand tile (the M or N index is the
+// contiguous one): blocks of 64 MN elements x 64 K rows, every K row 128 bytes with the
+// 128-byte swizzle.  Inside a block 8 K rows form one 1024-byte group (stride byte offset);
+// `mn_block_bytes` separates consecutive 64-element MN blocks (leading byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);          // start address  [0,14)
+  d |= static_cast<uint64_t>((mn_block_bytes >> 4) & 0x3FFFu) << 16; // leading byte offset [16,30)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                       // stride byte offset [32,46)
+  d |= static_cast<uint64_t>(1) << 46;                               // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                               // layout: SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A K-major, B K-major (b_mn_major = 0)
+// or MN-major (1).  `ab_format`: 0 = fp16, 1 = bf16.  M and N are the full (pair-wide) extents.
+__host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t ab_format, uint32_t m, uint32_t n,
+                                                      uint32_t b_mn_major = 0) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (b_mn_major << 16) | ((n >> 3) << 17) |
+         ((m >> 4) << 24);
 }
 
 }  // namespace sm100

@@ -72,6 +72,13 @@ def gemm_tn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" 
     return gemm_tn_test(A, B, out)
 
 
+def gemm_nn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" = None) -> "_torch.Tensor":
+    """``A[M,K] @ B[K,N]`` (B as ``torch.mm`` takes it) into ``out``; no transposed copy of B."""
+    if out is None:
+        out = _torch.empty((A.shape[0], B.shape[1]), dtype=A.dtype, device=A.device)
+    return _C.gemm_nn(A, B, out)
+
+
 class HostGemm:
     """``C_host = A_host @ B_host.T`` for operands and result in (pinned) HOST memory.
 
@@ -124,6 +131,6 @@ class HostGemm:
 from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, shard_rows  # noqa: E402
 
 __all__ = [
-    "gemm_tn_test", "gemm_tn", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
+    "gemm_tn_test", "gemm_tn", "gemm_nn", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
     "set_option", "set_trace_buffer", "trace_launch", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

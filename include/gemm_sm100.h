@@ -55,6 +55,15 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
                   long ldc, int dtype, void* workspace, size_t workspace_bytes, void* cuda_stream,
                   int* cuda_error_out);
 
+/* C[M,N] = A[M,K] * B[K,N]: the same kernels with B given row-major as [K, N] (N contiguous,
+ * pitch ldb >= N elements), i.e. without the transposed copy of B that the reference's callers
+ * make to reach its [N, K] contract (kernels/tests/gemm_bench.py:278-295,
+ * `B.t().contiguous()`).  B is loaded as 64-column blocks and handed to the tensor core as an
+ * MN-major operand.  Requirements as for gemm_sm100_tn with ldb % 8 == 0; needs no workspace
+ * (whole tiles only).  No reference counterpart: the reference implements the TN contract only. */
+int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                  int dtype, void* cuda_stream, int* cuda_error_out);
+
 /* C = A * B^T stored into `num_outputs` (1..8) output matrices at once: the epilogue issues one
  * TMA store per output for every finished tile.  All outputs share M, N, ldc and dtype; each
  * pointer must be 16-byte aligned and writable from the current device (its own memory, or a

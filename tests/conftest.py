@@ -46,6 +46,8 @@ def load_capi() -> ctypes.CDLL:
     I, L, P, Z = ctypes.c_int, ctypes.c_long, ctypes.c_void_p, ctypes.c_size_t
     lib.gemm_sm100_tn.argtypes = [P, P, P, I, I, I, L, L, L, I, P, Z, P, ctypes.POINTER(I)]
     lib.gemm_sm100_tn.restype = I
+    lib.gemm_sm100_nn.argtypes = [P, P, P, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]
+    lib.gemm_sm100_nn.restype = I
     lib.gemm_sm100_tn_fanout.argtypes = [P, P, ctypes.POINTER(P), I, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]
     lib.gemm_sm100_tn_fanout.restype = I
     lib.gemm_sm100_tn_static_scratch.argtypes = [P, P, P, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]

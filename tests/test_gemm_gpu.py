@@ -38,7 +38,7 @@ def _reset_options(capi):
     capi.gemm_sm100_set_option(b"tile_config", -1)
     capi.gemm_sm100_set_option(b"max_ctas", 0)
     capi.gemm_sm100_set_option(b"split_k", -1)
-    capi.gemm_sm100_set_option(b"k_rotate", -1)
+    capi.gemm_sm100_set_option(b"k_rotate", 0)
     capi.gemm_sm100_set_option(b"group_m", 0)
 
 
@@ -325,6 +325,56 @@ def test_split_k_rejects_missing_workspace(capi):
     rc = capi.gemm_sm100_tn(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0, None, 0, None,
                             ctypes.byref(err))
     assert rc == 7          # GEMM_SM100_ERR_WORKSPACE, nothing launched
+
+
+# --------------------------------------------------------------- B as [K, N]
+NN_SHAPES = [(256, 256, 64), (512, 768, 320), (300, 520, 72), (1024, 1024, 1024), (128, 4096, 512), (100, 264, 2056)]
+
+
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3])
+@pytest.mark.parametrize("shape", NN_SHAPES)
+def test_nn_layout_matches_oracle(gk, capi, config, shape):
+    """C = A[M,K] @ B[K,N] with B row-major as torch.mm takes it (loaded as an MN-major operand),
+    against the oracle on the transposed copy, and bitwise against the TN entry point."""
+    M, N, K = shape
+    A, Bt = oracle.make_inputs(M, N, K, 110 + M % 3)         # Bt is [N, K]
+    B = Bt.T.contiguous()                                      # [K, N]
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = gk.gemm_nn(A.cuda(), B.cuda(), C)
+    gk.device_status()
+    assert out.data_ptr() == C.data_ptr()
+    assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, Bt), torch.bfloat16)
+    C_tn = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A.cuda(), Bt.cuda(), C_tn)
+    gk.device_status()
+    assert torch.equal(C.view(torch.int16), C_tn.view(torch.int16))       # same products, same order
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("config", [0, 1, 2, 3])
+def test_nn_layout_exact_on_integers(gk, capi, dtype, config):
+    M, N, K = 384, 640, 256
+    A, Bt = oracle.make_ternary_inputs(M, N, K, 111, dtype)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = gk.gemm_nn(A.cuda(), Bt.T.contiguous().cuda())
+    gk.device_status()
+    assert torch.equal(C.cpu().view(torch.int16), oracle.c_gemm_tn(A, Bt).view(torch.int16))
+
+
+def test_nn_layout_row_pitched_b_and_one_hot(gk):
+    """B inside a wider buffer (pitch > N); A one-hot so that C rows are rows of B: a wrong block
+    or K-group offset in the MN-major descriptor moves whole 64-column blocks or 8-row groups."""
+    M, N, K = 256, 448, 192
+    ks = (torch.arange(M) * 5) % K
+    A = torch.zeros(M, K, dtype=torch.bfloat16)
+    A[torch.arange(M), ks] = 1.0
+    B = ((torch.arange(K).view(K, 1) * 7 + torch.arange(N).view(1, N)) % 253).to(torch.bfloat16)
+    wide = torch.zeros((K, N + 64), dtype=torch.bfloat16, device="cuda")
+    wide[:, 8:8 + N] = B.cuda()
+    C = gk.gemm_nn(A.cuda(), wide[:, 8:8 + N])
+    gk.device_status()
+    assert torch.equal(C.cpu().view(torch.int16), B[ks].contiguous().view(torch.int16))
 
 
 # ------------------------------------------------------------ several outputs
