@@ -54,18 +54,24 @@ def time_fn(fn, scratch, warmup=3, iters=10):
     return statistics.median(times), min(times)
 
 
-def bench_shape(M, N, K, dtype, scratch, peak):
+def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     A = (torch.randn((M, K), device="cuda") / K ** 0.5).to(dtype)
-    B = (torch.randn((N, K), device="cuda") / K ** 0.5).to(dtype)        # already [N, K]: no transpose copy
     C = torch.empty((M, N), device="cuda", dtype=dtype)
     C2 = torch.empty((M, N), device="cuda", dtype=dtype)
-    ours_med, ours_min = time_fn(lambda: gk.gemm_tn_test(A, B, C), scratch)
-    gk.device_status()
-    torch_med, torch_min = time_fn(lambda: torch.mm(A, B.T, out=C2), scratch)
+    if layout == "tn":
+        B = (torch.randn((N, K), device="cuda") / K ** 0.5).to(dtype)    # already [N, K]: no transpose copy
+        ours_med, ours_min = time_fn(lambda: gk.gemm_tn_test(A, B, C), scratch)
+        gk.device_status()
+        torch_med, torch_min = time_fn(lambda: torch.mm(A, B.T, out=C2), scratch)
+    else:
+        B = (torch.randn((K, N), device="cuda") / K ** 0.5).to(dtype)    # [K, N], as torch.mm takes it
+        ours_med, ours_min = time_fn(lambda: gk.gemm_nn(A, B, C), scratch)
+        gk.device_status()
+        torch_med, torch_min = time_fn(lambda: torch.mm(A, B, out=C2), scratch)
     flops = 2.0 * M * N * K
     nbytes = 2.0 * (M * K + N * K + M * N)
     rec = {
-        "M": M, "N": N, "K": K, "dtype": str(dtype).replace("torch.", ""),
+        "M": M, "N": N, "K": K, "dtype": str(dtype).replace("torch.", ""), "layout": layout,
         "ours_ms": round(ours_med, 4), "ours_min_ms": round(ours_min, 4), "torch_ms": round(torch_med, 4),
         "ours_tflops": round(flops / ours_med / 1e9, 1), "torch_tflops": round(flops / torch_med / 1e9, 1),
         "speedup_vs_torch": round(torch_med / ours_med, 3), "ours_gbs": round(nbytes / ours_med / 1e6, 1),
@@ -81,6 +87,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--quick", action="store_true", help="skip the largest shapes")
+    ap.add_argument("--layout", default="tn", choices=["tn", "nn"], help="B as [N,K] (tn) or as [K,N] (nn)")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     name, peak = peak_for_device()
@@ -91,7 +98,7 @@ def main():
         shapes = [s for s in shapes if 2.0 * s[0] * s[1] * s[2] < 2.5e12]
     print(f"{'M':>6} {'N':>6} {'K':>6} | {'ours ms':>9} {'TFLOP/s':>8} {'GB/s':>8} | {'torch ms':>9} {'TFLOP/s':>8} | speed-up")
     for (M, N, K) in shapes:
-        r = bench_shape(M, N, K, dtype, scratch, peak)
+        r = bench_shape(M, N, K, dtype, scratch, peak, args.layout)
         print(f"{M:>6} {N:>6} {K:>6} | {r['ours_ms']:>9.4f} {r['ours_tflops']:>8.1f} {r['ours_gbs']:>8.1f} | "
               f"{r['torch_ms']:>9.4f} {r['torch_tflops']:>8.1f} | {r['speedup_vs_torch']:.3f}x")
         print(json.dumps(r))
