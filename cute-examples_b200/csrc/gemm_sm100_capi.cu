@@ -169,6 +169,7 @@ struct Problem {
   long lda, ldb, ldc;
   int dtype;
   bool b_is_kn = false;   // B given as [K, N] (pitch ldb >= N) instead of [N, K]
+  bool a_is_km = false;   // A given as [K, M] (pitch lda >= M) instead of [M, K]
 };
 
 int validate(const Problem& p) {
@@ -177,7 +178,8 @@ int validate(const Problem& p) {
   if (p.M == 0 || p.N == 0) return GEMM_SM100_OK;
   if (!p.C || (p.K > 0 && (!p.A || !p.B))) return GEMM_SM100_ERR_NULL_POINTER;
   if (p.K % 8 != 0) return GEMM_SM100_ERR_BAD_SHAPE;
-  if (p.lda < p.K || p.ldb < (p.b_is_kn ? p.N : p.K) || p.ldc < p.N) return GEMM_SM100_ERR_BAD_SHAPE;
+  if (p.lda < (p.a_is_km ? p.M : p.K) || p.ldb < (p.b_is_kn ? p.N : p.K) || p.ldc < p.N)
+    return GEMM_SM100_ERR_BAD_SHAPE;
   if (p.lda % 8 != 0 || p.ldb % 8 != 0 || p.ldc % 8 != 0) return GEMM_SM100_ERR_BAD_ALIGNMENT;
   if ((reinterpret_cast<uintptr_t>(p.A) | reinterpret_cast<uintptr_t>(p.B) |
        reinterpret_cast<uintptr_t>(p.C)) & 15u)
@@ -437,27 +439,34 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
   return GEMM_SM100_OK;
 }
 
-// Launch of the B[K,N] variant (whole tiles only: no K-split, no trace instantiation).
+// Launch of the variants with B as [K,N] and / or A as [K,M] (whole tiles only: no K-split, no
+// trace instantiation).
 template <int kCfgIndex, bool kIsBf16>
 int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
   using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
-  auto kernel = gemm_nn_kernel<Cfg>;
+  auto kernel = p.a_is_km ? (p.b_is_kn ? gemm_layout_kernel<Cfg, true, true> : gemm_layout_kernel<Cfg, true, false>)
+                          : gemm_layout_kernel<Cfg, false, true>;
   constexpr int dt = kIsBf16 ? 0 : 1;
   cudaError_t e;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!st.nn_attr_set[kCfgIndex][dt]) {
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      for (auto k : {gemm_layout_kernel<Cfg, true, true>, gemm_layout_kernel<Cfg, true, false>,
+                     gemm_layout_kernel<Cfg, false, true>}) {
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      }
       st.nn_attr_set[kCfgIndex][dt] = true;
     }
   }
   const TileParams tp = base_tile_params<Cfg>(p, st);
   CUtensorMap map_a, map_b, map_c;
-  int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  int rc = p.a_is_km ? encode_2d(&map_a, p.A, p.dtype, p.K, p.M, p.lda, 64, cuda_error_out)   // K rows of M columns
+                     : encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
   if (rc) return rc;
-  rc = encode_2d(&map_b, p.B, p.dtype, p.K, p.N, p.ldb, 64, cuda_error_out);     // K rows of N columns
+  rc = p.b_is_kn ? encode_2d(&map_b, p.B, p.dtype, p.K, p.N, p.ldb, 64, cuda_error_out)       // K rows of N columns
+                 : encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
   if (rc) return rc;
   rc = encode_2d(&map_c, p.C, p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
   if (rc) return rc;
@@ -638,8 +647,15 @@ int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int
 
 int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                   int dtype, void* cuda_stream, int* cuda_error_out) {
+  return gemm_sm100_gemm(A, B, C, M, N, K, lda, ldb, ldc, dtype, 0, 1, cuda_stream, cuda_error_out);
+}
+
+int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                    int dtype, int a_is_km, int b_is_kn, void* cuda_stream, int* cuda_error_out) {
   if (cuda_error_out) *cuda_error_out = 0;
-  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype, true};
+  if (!a_is_km && !b_is_kn)
+    return gemm_sm100_tn(A, B, C, M, N, K, lda, ldb, ldc, dtype, nullptr, 0, cuda_stream, cuda_error_out);
+  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype, b_is_kn != 0, a_is_km != 0};
   int rc = validate(p);
   if (rc != GEMM_SM100_OK) return rc;
   if (M == 0 || N == 0) return GEMM_SM100_OK;

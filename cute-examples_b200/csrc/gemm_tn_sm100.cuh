@@ -289,7 +289,8 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
 // kBIsKN: B is given as [K, N] (N contiguous, the "NN" product A * B) instead of [N, K].  Only the
 // B loads and the B descriptors change: a stage then holds B as 64-column blocks of 64 K rows
 // (one TMA box each), described to the tensor core as an MN-major operand.
-template <class Cfg, bool kDebug, bool kSplitK, bool kBIsKN = false>
+// kAIsKM: likewise A given as [K, M] (M contiguous), i.e. the product A^T * B.
+template <class Cfg, bool kDebug, bool kSplitK, bool kBIsKN = false, bool kAIsKM = false>
 __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                              const CUtensorMap* tmap_c, const int num_c, const TileParams& p) {
   constexpr int G = Cfg::kCtaGroup;
@@ -426,7 +427,15 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           const int x = kb_phys * Cfg::kBlockK;
           if (issuer) {
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
-            tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
+            if constexpr (!kAIsKM) {
+              tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
+            } else {
+              // A[K, M]: coordinates are (row of C, K); two 64 x 64 boxes cover the CTA's 128 rows
+#pragma unroll
+              for (int j = 0; j < Cfg::kBlockM / 64; ++j)
+                tma_load_2d<G>(smem_a + s * Cfg::kABytes + j * 8192, &tmap_a, full_leader + 8u * s,
+                               row_a + j * 64, x, pol);
+            }
 #pragma unroll
             for (int h = 0; h < Cfg::kHalves; ++h) {
               if constexpr (!kBIsKN) {
@@ -466,8 +475,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       bool peer_ready = true;
       if constexpr (G == 2) peer_ready = wait_bounded(bar_base + kTmemReadyOff, 0u, ctx, kStatusTimeoutMmaAcc + 0xf);
       constexpr uint32_t idesc =
-          make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN, kBIsKN ? 1u : 0u);
-      const uint64_t da0 = make_smem_desc_sw128(smem_a);
+          make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN, kBIsKN ? 1u : 0u, kAIsKM ? 1u : 0u);
+      const uint64_t da0 = kAIsKM ? make_smem_desc_sw128_mn(smem_a, 8192) : make_smem_desc_sw128(smem_a);
+      constexpr uint32_t kAStepK = kAIsKM ? 128u : 2u;
       const uint64_t db0 = kBIsKN ? make_smem_desc_sw128_mn(smem_b, 8192) : make_smem_desc_sw128(smem_b);
       // start-address step (16-byte units) of B per 16-element K step: 32 bytes along a K-major row,
       // two 8-row groups of 1024 bytes for the MN-major layout
@@ -531,7 +541,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
                 umma_f16<G>(tmem_d, da, db, idesc, first_kb ? 0u : 1u);   // first K step of a segment overwrites
 #pragma unroll
                 for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k)
-                  umma_f16<G>(tmem_d, da + 2u * k, db + kBStepK * k, idesc, 1u);
+                  umma_f16<G>(tmem_d, da + kAStepK * k, db + kBStepK * k, idesc, 1u);
               }
               if (last_kb) {                                             // this half's accumulator is complete
                 if (skip_mma) {
@@ -775,12 +785,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   gemm_tn_body<Cfg, kDebug, kSplitK>(tmap_a, tmap_b, &tmap_c, 1, p);
 }
 
-// C = A[M,K] * B[K,N]: same kernel, B loaded and described as an MN-major operand.
-template <class Cfg>
+// The other operand layouts: same kernel, B given as [K,N] and / or A given as [K,M], loaded and
+// described as MN-major operands.
+template <class Cfg, bool kAIsKM, bool kBIsKN>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
-gemm_nn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
-  gemm_tn_body<Cfg, false, false, true>(tmap_a, tmap_b, &tmap_c, 1, p);
+gemm_layout_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
+  gemm_tn_body<Cfg, false, false, kBIsKN, kAIsKM>(tmap_a, tmap_b, &tmap_c, 1, p);
 }
 
 // Self-test of the bounded wait: one warp waits on a barrier that nothing ever arrives on.  The

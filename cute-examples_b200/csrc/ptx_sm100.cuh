@@ -326,12 +326,12 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, 
   return d;
 }
 
-// Instruction descriptor for kind::f16: fp32 accumulate, A K-major, B K-major (b_mn_major = 0)
-// or MN-major (1).  `ab_format`: 0 = fp16, 1 = bf16.  M and N are the full (pair-wide) extents.
+// Instruction descriptor for kind::f16: fp32 accumulate; A and B each K-major (0) or MN-major (1).
+// `ab_format`: 0 = fp16, 1 = bf16.  M and N are the full (pair-wide) extents.
 __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t ab_format, uint32_t m, uint32_t n,
-                                                      uint32_t b_mn_major = 0) {
-  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (b_mn_major << 16) | ((n >> 3) << 17) |
-         ((m >> 4) << 24);
+                                                      uint32_t b_mn_major = 0, uint32_t a_mn_major = 0) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
+         ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 }  // namespace sm100

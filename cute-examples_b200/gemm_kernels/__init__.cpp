@@ -85,38 +85,48 @@ torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::
   return C;
 }
 
-// C[M,N] = A[M,K] * B[K,N] (B row-major with N contiguous): no transposed copy of B is needed.
-torch::Tensor gemm_nn(const torch::Tensor A, const torch::Tensor B, torch::Tensor C) {
+// C[M,N] = op(A) * op(B) for the four operand layouts: A as [M,K] or [K,M] (a_is_km), B as [N,K] or
+// [K,N] (b_is_kn).  No transposed copies are made; the [K,*] forms go to the tensor core as
+// MN-major operands.
+torch::Tensor gemm_layouts(const torch::Tensor A, const torch::Tensor B, torch::Tensor C, bool a_is_km,
+                           bool b_is_kn) {
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2, "All tensors must be 2D (matrix) tensors");
   TORCH_CHECK((A.numel() == 0 || A.stride(1) == 1) && (B.numel() == 0 || B.stride(1) == 1) &&
                   (C.numel() == 0 || C.stride(1) == 1),
               "All tensors must have unit stride along their last dimension");
-  TORCH_CHECK(A.size(1) == B.size(0), "Inner dimensions of A and B must match (A: ", A.size(1),
-              ", B: ", B.size(0), ")");
+  const int64_t M = a_is_km ? A.size(1) : A.size(0);
+  const int64_t Ka = a_is_km ? A.size(0) : A.size(1);
+  const int64_t N = b_is_kn ? B.size(1) : B.size(0);
+  const int64_t Kb = b_is_kn ? B.size(0) : B.size(1);
+  TORCH_CHECK(Ka == Kb, "Inner dimensions of A and B must match (A: ", Ka, ", B: ", Kb, ")");
   const int dtype = dtype_code(A);
   TORCH_CHECK(B.scalar_type() == A.scalar_type() && C.scalar_type() == A.scalar_type(),
               "A, B and C must have the same dtype");
-  TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(1), "C must be of shape [A.size(0), B.size(1)]");
-  TORCH_CHECK(A.size(0) <= INT32_MAX && B.size(1) <= INT32_MAX && A.size(1) <= INT32_MAX,
-              "extents must fit in 32 bits");
+  TORCH_CHECK(C.size(0) == M && C.size(1) == N, "C must be of shape [", M, ", ", N, "]");
+  TORCH_CHECK(M <= INT32_MAX && N <= INT32_MAX && Ka <= INT32_MAX, "extents must fit in 32 bits");
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "All tensors must be CUDA tensors");
   TORCH_CHECK(A.device() == B.device() && A.device() == C.device(), "All tensors must be on the same device");
-  const int M = static_cast<int>(A.size(0)), N = static_cast<int>(B.size(1)), K = static_cast<int>(A.size(1));
   if (M == 0 || N == 0) return C;
+  if (!a_is_km && !b_is_kn) return gemm_tn_test(A, B, C);
   c10::cuda::CUDAGuard guard(A.device());
   cudaStream_t stream = c10::cuda::getCurrentCUDAStream(A.device().index()).stream();
-  const long lda = M > 1 ? static_cast<long>(A.stride(0)) : static_cast<long>(K);
-  const long ldb = K > 1 ? static_cast<long>(B.stride(0)) : static_cast<long>(N);
+  const long lda = A.size(0) > 1 ? static_cast<long>(A.stride(0)) : static_cast<long>(A.size(1));
+  const long ldb = B.size(0) > 1 ? static_cast<long>(B.stride(0)) : static_cast<long>(B.size(1));
   const long ldc = M > 1 ? static_cast<long>(C.stride(0)) : static_cast<long>(N);
   int cuda_error = 0;
   int rc;
   {
     pybind11::gil_scoped_release release;
-    rc = gemm_sm100_nn(A.const_data_ptr(), B.const_data_ptr(), C.mutable_data_ptr(), M, N, K, lda, ldb, ldc, dtype,
-                       static_cast<void*>(stream), &cuda_error);
+    rc = gemm_sm100_gemm(A.const_data_ptr(), B.const_data_ptr(), C.mutable_data_ptr(), static_cast<int>(M),
+                         static_cast<int>(N), static_cast<int>(Ka), lda, ldb, ldc, dtype, a_is_km ? 1 : 0,
+                         b_is_kn ? 1 : 0, static_cast<void*>(stream), &cuda_error);
   }
-  raise_for(rc, cuda_error, "gemm_nn");
+  raise_for(rc, cuda_error, "gemm_layouts");
   return C;
+}
+
+torch::Tensor gemm_nn(const torch::Tensor A, const torch::Tensor B, torch::Tensor C) {
+  return gemm_layouts(A, B, C, false, true);
 }
 
 // A * B^T stored through raw device pointers into several outputs of shape [M, N] with row pitch
@@ -191,6 +201,8 @@ std::string describe_config(int index) {
 PYBIND11_MODULE(_C, m) {
   m.def("gemm_tn_test", &gemm_tn_test, "GEMM transpose-normal test function", pybind11::arg("A"),
         pybind11::arg("B"), pybind11::arg("C"));
+  m.def("gemm_layouts", &gemm_layouts, "C = op(A) * op(B): A as [M,K] or [K,M], B as [N,K] or [K,N]",
+        pybind11::arg("A"), pybind11::arg("B"), pybind11::arg("C"), pybind11::arg("a_is_km"), pybind11::arg("b_is_kn"));
   m.def("gemm_nn", &gemm_nn, "C = A[M,K] * B[K,N] into the caller's C", pybind11::arg("A"), pybind11::arg("B"),
         pybind11::arg("C"));
   m.def("gemm_tn_fanout", &gemm_tn_fanout, "A * B^T stored into several outputs given as device addresses",

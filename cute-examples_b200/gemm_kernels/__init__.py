@@ -79,6 +79,18 @@ def gemm_nn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" 
     return _C.gemm_nn(A, B, out)
 
 
+def gemm(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" = None, a_is_km: bool = False,
+         b_is_kn: bool = True) -> "_torch.Tensor":
+    """``op(A) @ op(B)`` for all four operand layouts without transposed copies: A is ``[M,K]`` or, with
+    ``a_is_km``, ``[K,M]``; B is ``[K,N]`` (the default, as ``torch.mm`` takes it) or, with
+    ``b_is_kn=False``, ``[N,K]`` (the layout of ``gemm_tn_test``)."""
+    M = A.shape[1] if a_is_km else A.shape[0]
+    N = B.shape[1] if b_is_kn else B.shape[0]
+    if out is None:
+        out = _torch.empty((M, N), dtype=A.dtype, device=A.device)
+    return _C.gemm_layouts(A, B, out, a_is_km, b_is_kn)
+
+
 class HostGemm:
     """``C_host = A_host @ B_host.T`` for operands and result in (pinned) HOST memory.
 
@@ -131,6 +143,6 @@ class HostGemm:
 from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, shard_rows  # noqa: E402
 
 __all__ = [
-    "gemm_tn_test", "gemm_tn", "gemm_nn", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
+    "gemm_tn_test", "gemm_tn", "gemm_nn", "gemm", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
     "set_option", "set_trace_buffer", "trace_launch", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

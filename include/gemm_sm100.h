@@ -64,6 +64,14 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
 int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                   int dtype, void* cuda_stream, int* cuda_error_out);
 
+/* All four operand layouts behind one call: A as [M,K] (a_is_km = 0) or [K,M] (1, pitch
+ * lda >= M), B as [N,K] (b_is_kn = 0) or [K,N] (1, pitch ldb >= N).  (0,0) is gemm_sm100_tn
+ * without a workspace (so shapes for which gemm_sm100_workspace_bytes is non-zero are refused
+ * there: call gemm_sm100_tn for those), (0,1) is gemm_sm100_nn.  The [K,*] forms are loaded as
+ * MN-major operands; whole tiles only.  No reference counterpart (TN only). */
+int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                    int dtype, int a_is_km, int b_is_kn, void* cuda_stream, int* cuda_error_out);
+
 /* C = A * B^T stored into `num_outputs` (1..8) output matrices at once: the epilogue issues one
  * TMA store per output for every finished tile.  All outputs share M, N, ldc and dtype; each
  * pointer must be 16-byte aligned and writable from the current device (its own memory, or a

@@ -362,6 +362,40 @@ def test_nn_layout_exact_on_integers(gk, capi, dtype, config):
     assert torch.equal(C.cpu().view(torch.int16), oracle.c_gemm_tn(A, Bt).view(torch.int16))
 
 
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3])
+@pytest.mark.parametrize("a_is_km,b_is_kn", [(True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 320), (304, 520, 72), (128, 1024, 512)])   # M % 8 == 0: A^T rows are M long
+def test_transposed_a_layouts(gk, capi, shape, a_is_km, b_is_kn, config):
+    """A given as [K, M] (and B as [N, K] or [K, N]): bit-identical to the TN entry point on the
+    re-laid-out operands, and inside the tolerance against the oracle."""
+    M, N, K = shape
+    A, Bt = oracle.make_inputs(M, N, K, 120)
+    Ain = A.T.contiguous().cuda() if a_is_km else A.cuda()
+    Bin = Bt.T.contiguous().cuda() if b_is_kn else Bt.cuda()
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gk.gemm(Ain, Bin, C, a_is_km=a_is_km, b_is_kn=b_is_kn)
+    gk.device_status()
+    assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, Bt), torch.bfloat16)
+    C_tn = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A.cuda(), Bt.cuda(), C_tn)
+    gk.device_status()
+    assert torch.equal(C.view(torch.int16), C_tn.view(torch.int16))
+
+
+def test_transposed_a_exact_one_hot(gk):
+    """A^T one-hot in [K, M] form: C rows are rows of B; catches a wrong 64-row block or K-group
+    offset in A's MN-major descriptor."""
+    M, N, K = 384, 320, 192
+    ks = (torch.arange(M) * 5) % K
+    A = torch.zeros(M, K, dtype=torch.float16)
+    A[torch.arange(M), ks] = 1.0
+    B = ((torch.arange(K).view(K, 1) * 7 + torch.arange(N).view(1, N)) % 253).to(torch.float16)     # [K, N]
+    C = gk.gemm(A.T.contiguous().cuda(), B.cuda(), a_is_km=True, b_is_kn=True)
+    gk.device_status()
+    assert torch.equal(C.cpu().view(torch.int16), B[ks].contiguous().view(torch.int16))
+
+
 def test_nn_layout_row_pitched_b_and_one_hot(gk):
     """B inside a wider buffer (pitch > N); A one-hot so that C rows are rows of B: a wrong block
     or K-group offset in the MN-major descriptor moves whole 64-column blocks or 8-row groups."""
