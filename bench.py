@@ -44,6 +44,13 @@ import torch  # noqa: E402
 # dram__bytes_write.sum from an ncu capture of this kernel on this workload, mean of two launches.
 NCU_DRAM_BYTES_PER_LAUNCH_8192 = 985_000_000
 
+WORKLOAD_SINGLE = "cfg2 square bf16 TN GEMM M=N=K=8192, fp32 accumulate, bf16 out, seed 1"
+
+
+def workload_multi(world: int) -> str:
+    return f"cfg5 bf16 TN GEMM M=N=K=32768, seed 4, B row-sharded over {world} GPUs, C assembled on every GPU"
+
+
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
 
@@ -266,10 +273,10 @@ def run_reference(args, rank):
 
     if args.gpus == 1:
         M = N = K = 8192
-        seed, workload = 1, "cfg2 square bf16 GEMM M=N=K=8192"
+        seed, workload = 1, WORKLOAD_SINGLE
     else:
         M = N = K = 32768
-        seed, workload = 4, f"cfg5 bf16 GEMM M=N=K=32768, N-split over {args.gpus} GPUs + all-gather of C"
+        seed, workload = 4, workload_multi(args.gpus)
     rows = 1024 if args.gpus == 1 else 256
     A, B = oracle.make_inputs(rows, N, K, seed, torch.bfloat16)
     for _ in range(min(args.warmup, 2)):
@@ -285,7 +292,8 @@ def run_reference(args, rank):
         "impl": "reference", "metric": "bf16 GEMM TFLOP/s", "value": round(tf, 4), "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": workload, "sample_rows": rows},
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "M": M, "N": N, "K": K, "sample_rows": rows},
         "cpu_baseline": {"value": round(tf, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": sample},
         "e2e": {"value": round(tf, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -349,7 +357,7 @@ def run_single(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "cfg2 square bf16 TN GEMM M=N=K=8192, fp32 accumulate, bf16 out, seed 1",
+        "config": {"workload": WORKLOAD_SINGLE,
                    "M": M, "N": N, "K": K, "tile_config": gk.describe_config(gk.select_config(M, N, K, 0)),
                    "l2": "operands 256 MiB > 126 MB L2 (inputs larger than L2; no flush between steps)"},
         "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
@@ -475,7 +483,7 @@ def run_multi(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"cfg5 bf16 TN GEMM M=N=K=32768, B row-sharded over {world} GPUs, {how}",
+            "config": {"workload": workload_multi(world), "exchange": how,
                        "M": M, "N": N, "K": K, "nsplit_mode": mode,
                        "per_gpu_tflops": round(per_gpu, 2),
                        "local_gemm_ms_per_step": round(local_ms, 4),
