@@ -120,6 +120,10 @@ int get_encoder(int* cuda_error_out) {
   return GEMM_SM100_OK;
 }
 
+// Columns of C the TMA stores cover: whole 16-byte pieces only (the kernel writes the last N % 8
+// columns with plain stores); never 0, which is not a valid extent (the map is unused then).
+inline long tma_store_cols(long n) { return n >= 8 ? (n & ~7L) : 8; }
+
 // Tensor map of a row-major 2-D array of 16-bit elements: `rows` x `cols`, pitch `ld`
 // elements, box `box_rows` x 64 columns, 128-byte swizzle (64 x 2 B = one swizzle row).
 int encode_2d(CUtensorMap* map, const void* base, int dtype, long rows, long cols, long ld,
@@ -170,6 +174,8 @@ struct Problem {
   int dtype;
   bool b_is_kn = false;   // B given as [K, N] (pitch ldb >= N) instead of [N, K]
   bool a_is_km = false;   // A given as [K, M] (pitch lda >= M) instead of [M, K]
+  float alpha = 1.0f;     // C = alpha * op(A) op(B) + beta * C (only the layout kernels apply them)
+  float beta = 0.0f;
 };
 
 int validate(const Problem& p) {
@@ -286,6 +292,10 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.sk_partials = nullptr;
   tp.sk_rows = 128;
   tp.k_rotate = 0;
+  tp.alpha = p.alpha;
+  tp.beta = p.beta;
+  tp.c_ptr = p.C;
+  tp.ldc = p.ldc;
   return tp;
 }
 
@@ -356,7 +366,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   if (rc) return rc;
   rc = encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
   if (rc) return rc;
-  rc = encode_2d(&map_c, p.C, p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
+  rc = encode_2d(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
   if (rc) return rc;
 
   long ctas = plan.ctas;
@@ -446,14 +456,14 @@ int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t 
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
   using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
   auto kernel = p.a_is_km ? (p.b_is_kn ? gemm_layout_kernel<Cfg, true, true> : gemm_layout_kernel<Cfg, true, false>)
-                          : gemm_layout_kernel<Cfg, false, true>;
+                          : (p.b_is_kn ? gemm_layout_kernel<Cfg, false, true> : gemm_layout_kernel<Cfg, false, false>);
   constexpr int dt = kIsBf16 ? 0 : 1;
   cudaError_t e;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!st.nn_attr_set[kCfgIndex][dt]) {
       for (auto k : {gemm_layout_kernel<Cfg, true, true>, gemm_layout_kernel<Cfg, true, false>,
-                     gemm_layout_kernel<Cfg, false, true>}) {
+                     gemm_layout_kernel<Cfg, false, true>, gemm_layout_kernel<Cfg, false, false>}) {
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
       }
@@ -468,7 +478,7 @@ int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t 
   rc = p.b_is_kn ? encode_2d(&map_b, p.B, p.dtype, p.K, p.N, p.ldb, 64, cuda_error_out)       // K rows of N columns
                  : encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
   if (rc) return rc;
-  rc = encode_2d(&map_c, p.C, p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
+  rc = encode_2d(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
   if (rc) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(plan.ctas));
@@ -622,7 +632,7 @@ int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int
     if (rc != GEMM_SM100_OK) return rc;
   }
   if (M == 0 || N == 0) return GEMM_SM100_OK;
-  if (K == 0) return GEMM_SM100_ERR_BAD_SHAPE;
+  if (K == 0 || N % 8 != 0) return GEMM_SM100_ERR_BAD_SHAPE;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   DeviceState* st = nullptr;
   {
@@ -652,14 +662,22 @@ int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, lo
 
 int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                     int dtype, int a_is_km, int b_is_kn, void* cuda_stream, int* cuda_error_out) {
+  return gemm_sm100_gemm_scaled(A, B, C, M, N, K, lda, ldb, ldc, dtype, a_is_km, b_is_kn, 1.0f, 0.0f, cuda_stream,
+                                cuda_error_out);
+}
+
+int gemm_sm100_gemm_scaled(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
+                           long ldc, int dtype, int a_is_km, int b_is_kn, float alpha, float beta,
+                           void* cuda_stream, int* cuda_error_out) {
   if (cuda_error_out) *cuda_error_out = 0;
-  if (!a_is_km && !b_is_kn)
+  if (!a_is_km && !b_is_kn && alpha == 1.0f && beta == 0.0f)
     return gemm_sm100_tn(A, B, C, M, N, K, lda, ldb, ldc, dtype, nullptr, 0, cuda_stream, cuda_error_out);
-  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype, b_is_kn != 0, a_is_km != 0};
+  Problem p{A, B, C, M, N, K, lda, ldb, ldc, dtype, b_is_kn != 0, a_is_km != 0, alpha, beta};
   int rc = validate(p);
   if (rc != GEMM_SM100_OK) return rc;
   if (M == 0 || N == 0) return GEMM_SM100_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (K == 0 && beta != 0.0f) return GEMM_SM100_ERR_BAD_SHAPE;   // beta * C alone is not a GEMM
   if (K == 0) {
     cudaError_t e = cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 2, 0, static_cast<size_t>(N) * 2,
                                       static_cast<size_t>(M), stream);
@@ -674,7 +692,7 @@ int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, 
     if (rc != GEMM_SM100_OK) return rc;
   }
   Plan plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false);
-  if (plan.config > 3) plan = Plan{};       // the experimental configurations have no B[K,N] variant
+  if (plan.config > 3) plan = Plan{};       // the experimental configurations have no such variant
   if (plan.ctas == 0) {
     const long tiles = ceil_div(M, 256L) * ceil_div(N, 256L);
     const long slots = st->sm_count / 2;

@@ -71,6 +71,10 @@ struct TileParams {
   // read exactly once (a single tile row, the memory-bound small-M case): the CTAs then stream
   // different column offsets at any moment, which spreads the requests over the DRAM channels.
   int k_rotate;
+  // Optional epilogue scaling (kernels instantiated with kScaled only): C = alpha * acc + beta * C.
+  float alpha, beta;
+  void* c_ptr;                     // C as the caller passed it: read when beta != 0, and written with
+  long long ldc;                   // plain stores in its last N % 8 columns; row pitch in elements
 };
 
 // Experiment switches (results are garbage with any of them set).
@@ -290,7 +294,9 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
 // B loads and the B descriptors change: a stage then holds B as 64-column blocks of 64 K rows
 // (one TMA box each), described to the tensor core as an MN-major operand.
 // kAIsKM: likewise A given as [K, M] (M contiguous), i.e. the product A^T * B.
-template <class Cfg, bool kDebug, bool kSplitK, bool kBIsKN = false, bool kAIsKM = false>
+// kScaled: the epilogue applies alpha and beta (the reference has neither: gemm.cuh:368-377 only
+// converts the accumulator).
+template <class Cfg, bool kDebug, bool kSplitK, bool kBIsKN = false, bool kAIsKM = false, bool kScaled = false>
 __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                              const CUtensorMap* tmap_c, const int num_c, const TileParams& p) {
   constexpr int G = Cfg::kCtaGroup;
@@ -673,6 +679,52 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               }
             }
           }
+          if constexpr (kScaled) {
+            const int col = col0 + c * Cfg::kEpiCols;
+            if ((p.alpha != 1.0f || p.beta != 0.0f) && row0 + (int)lane < p.M && col < p.N) {
+              const float alpha = p.alpha, beta = p.beta;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                v0[i] = __float_as_uint(__uint_as_float(v0[i]) * alpha);
+                v1[i] = __float_as_uint(__uint_as_float(v1[i]) * alpha);
+              }
+              if (beta != 0.0f) {
+                // Old C of this thread's row in 16-byte pieces; the piece that straddles N (N not a
+                // multiple of 8) is read element by element, so nothing past C[row, N-1] is touched.
+                const uint16_t* crow = reinterpret_cast<const uint16_t*>(p.c_ptr) +
+                                       (long long)(row0 + (int)lane) * p.ldc + col;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if (col + 8 * j < p.N) {
+                    uint32_t w[4] = {0u, 0u, 0u, 0u};
+                    if (col + 8 * j + 8 <= p.N) {
+                      const uint4 old = *reinterpret_cast<const uint4*>(crow + 8 * j);
+                      w[0] = old.x, w[1] = old.y, w[2] = old.z, w[3] = old.w;
+                    } else {
+#pragma unroll
+                      for (int t = 0; t < 8; ++t)
+                        if (col + 8 * j + t < p.N) w[t >> 1] |= (uint32_t)crow[8 * j + t] << (16 * (t & 1));
+                    }
+                    uint32_t* v = (j < 4) ? &v0[8 * j] : &v1[8 * (j - 4)];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                      float lo, hi;
+                      if constexpr (Cfg::kIsBf16) {
+                        lo = __uint_as_float(w[t] << 16);
+                        hi = __uint_as_float(w[t] & 0xffff0000u);
+                      } else {
+                        const __half2 h2 = *reinterpret_cast<const __half2*>(&w[t]);
+                        lo = __low2float(h2);
+                        hi = __high2float(h2);
+                      }
+                      v[2 * t] = __float_as_uint(fmaf(beta, lo, __uint_as_float(v[2 * t])));
+                      v[2 * t + 1] = __float_as_uint(fmaf(beta, hi, __uint_as_float(v[2 * t + 1])));
+                    }
+                  }
+                }
+              }
+            }
+          }
           const bool live = (row0 < p.M) && (col0 + c * Cfg::kEpiCols < p.N) &&
                             !(kDebug && (dbg & kDebugSkipStores));
           if (live) {
@@ -695,10 +747,29 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             }
             fence_proxy_async_smem();
             __syncwarp();
+            // The output's tensor map ends at the last whole 16-byte piece of a row (a TMA store
+            // that crosses the end of the tensor inside a piece was seen to write the whole piece,
+            // zeroing up to 7 elements of the caller's memory past column N-1).  The N % 8 columns
+            // after it go out as 2-byte stores, each thread re-reading its own staged piece.
+            const int n_floor = p.N & ~7;
+            const int colc = col0 + c * Cfg::kEpiCols;
+            if (p.N != n_floor && colc <= n_floor && n_floor < colc + Cfg::kEpiCols && row_live) {
+              const uint32_t j = (uint32_t)(n_floor - colc) >> 3;
+              uint32_t w[4];
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                           : "r"(dst + ((j ^ (lane & 7u)) << 4))
+                           : "memory");
+              uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)(row0 + (int)lane) * p.ldc + n_floor;
+#pragma unroll
+              for (int t = 0; t < 7; ++t)
+                if (t < p.N - n_floor) crow[t] = (uint16_t)(w[t >> 1] >> (16 * (t & 1)));
+            }
             if (lane == 0) {
-              for (int d = 0; d < num_c; ++d)
-                tma_store_2d(tmap_c + d, stage_buf + buf * Cfg::kEpiWarpBuf, col0 + c * Cfg::kEpiCols, row0);
-              tma_store_commit();
+              if (colc < n_floor)
+                for (int d = 0; d < num_c; ++d)
+                  tma_store_2d(tmap_c + d, stage_buf + buf * Cfg::kEpiWarpBuf, colc, row0);
+              tma_store_commit();                              // also when empty: one group per buffer use
             }
             if constexpr (Cfg::kEpiBufs == 2) buf ^= 1u;
           }
@@ -787,11 +858,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 // The other operand layouts: same kernel, B given as [K,N] and / or A given as [K,M], loaded and
 // described as MN-major operands.
+// These instantiations also carry the alpha / beta epilogue (a run-time test per chunk).
 template <class Cfg, bool kAIsKM, bool kBIsKN>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_layout_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const __grid_constant__ CUtensorMap tmap_c, const TileParams p) {
-  gemm_tn_body<Cfg, false, false, kBIsKN, kAIsKM>(tmap_a, tmap_b, &tmap_c, 1, p);
+  gemm_tn_body<Cfg, false, false, kBIsKN, kAIsKM, true>(tmap_a, tmap_b, &tmap_c, 1, p);
 }
 
 // Self-test of the bounded wait: one warp waits on a barrier that nothing ever arrives on.  The

@@ -89,7 +89,7 @@ torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::
 // [K,N] (b_is_kn).  No transposed copies are made; the [K,*] forms go to the tensor core as
 // MN-major operands.
 torch::Tensor gemm_layouts(const torch::Tensor A, const torch::Tensor B, torch::Tensor C, bool a_is_km,
-                           bool b_is_kn) {
+                           bool b_is_kn, double alpha = 1.0, double beta = 0.0) {
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2, "All tensors must be 2D (matrix) tensors");
   TORCH_CHECK((A.numel() == 0 || A.stride(1) == 1) && (B.numel() == 0 || B.stride(1) == 1) &&
                   (C.numel() == 0 || C.stride(1) == 1),
@@ -107,7 +107,7 @@ torch::Tensor gemm_layouts(const torch::Tensor A, const torch::Tensor B, torch::
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda(), "All tensors must be CUDA tensors");
   TORCH_CHECK(A.device() == B.device() && A.device() == C.device(), "All tensors must be on the same device");
   if (M == 0 || N == 0) return C;
-  if (!a_is_km && !b_is_kn) return gemm_tn_test(A, B, C);
+  if (!a_is_km && !b_is_kn && alpha == 1.0 && beta == 0.0) return gemm_tn_test(A, B, C);
   c10::cuda::CUDAGuard guard(A.device());
   cudaStream_t stream = c10::cuda::getCurrentCUDAStream(A.device().index()).stream();
   const long lda = A.size(0) > 1 ? static_cast<long>(A.stride(0)) : static_cast<long>(A.size(1));
@@ -117,9 +117,10 @@ torch::Tensor gemm_layouts(const torch::Tensor A, const torch::Tensor B, torch::
   int rc;
   {
     pybind11::gil_scoped_release release;
-    rc = gemm_sm100_gemm(A.const_data_ptr(), B.const_data_ptr(), C.mutable_data_ptr(), static_cast<int>(M),
-                         static_cast<int>(N), static_cast<int>(Ka), lda, ldb, ldc, dtype, a_is_km ? 1 : 0,
-                         b_is_kn ? 1 : 0, static_cast<void*>(stream), &cuda_error);
+    rc = gemm_sm100_gemm_scaled(A.const_data_ptr(), B.const_data_ptr(), C.mutable_data_ptr(), static_cast<int>(M),
+                                static_cast<int>(N), static_cast<int>(Ka), lda, ldb, ldc, dtype, a_is_km ? 1 : 0,
+                                b_is_kn ? 1 : 0, static_cast<float>(alpha), static_cast<float>(beta),
+                                static_cast<void*>(stream), &cuda_error);
   }
   raise_for(rc, cuda_error, "gemm_layouts");
   return C;
@@ -201,8 +202,10 @@ std::string describe_config(int index) {
 PYBIND11_MODULE(_C, m) {
   m.def("gemm_tn_test", &gemm_tn_test, "GEMM transpose-normal test function", pybind11::arg("A"),
         pybind11::arg("B"), pybind11::arg("C"));
-  m.def("gemm_layouts", &gemm_layouts, "C = op(A) * op(B): A as [M,K] or [K,M], B as [N,K] or [K,N]",
-        pybind11::arg("A"), pybind11::arg("B"), pybind11::arg("C"), pybind11::arg("a_is_km"), pybind11::arg("b_is_kn"));
+  m.def("gemm_layouts", &gemm_layouts,
+        "C = alpha * op(A) * op(B) + beta * C: A as [M,K] or [K,M], B as [N,K] or [K,N]",
+        pybind11::arg("A"), pybind11::arg("B"), pybind11::arg("C"), pybind11::arg("a_is_km"), pybind11::arg("b_is_kn"),
+        pybind11::arg("alpha") = 1.0, pybind11::arg("beta") = 0.0);
   m.def("gemm_nn", &gemm_nn, "C = A[M,K] * B[K,N] into the caller's C", pybind11::arg("A"), pybind11::arg("B"),
         pybind11::arg("C"));
   m.def("gemm_tn_fanout", &gemm_tn_fanout, "A * B^T stored into several outputs given as device addresses",

@@ -80,15 +80,19 @@ def gemm_nn(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" 
 
 
 def gemm(A: "_torch.Tensor", B: "_torch.Tensor", out: "_torch.Tensor | None" = None, a_is_km: bool = False,
-         b_is_kn: bool = True) -> "_torch.Tensor":
-    """``op(A) @ op(B)`` for all four operand layouts without transposed copies: A is ``[M,K]`` or, with
-    ``a_is_km``, ``[K,M]``; B is ``[K,N]`` (the default, as ``torch.mm`` takes it) or, with
-    ``b_is_kn=False``, ``[N,K]`` (the layout of ``gemm_tn_test``)."""
+         b_is_kn: bool = True, alpha: float = 1.0, beta: float = 0.0) -> "_torch.Tensor":
+    """``alpha * op(A) @ op(B) + beta * out`` for all four operand layouts without transposed copies:
+    A is ``[M,K]`` or, with ``a_is_km``, ``[K,M]``; B is ``[K,N]`` (the default, as ``torch.mm`` takes
+    it) or, with ``b_is_kn=False``, ``[N,K]`` (the layout of ``gemm_tn_test``).  ``alpha`` and ``beta``
+    are applied to the fp32 accumulator before the one rounding to the output type (``torch.addmm``
+    semantics); ``beta != 0`` needs ``out``."""
     M = A.shape[1] if a_is_km else A.shape[0]
     N = B.shape[1] if b_is_kn else B.shape[0]
     if out is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 reads `out`: pass it")
         out = _torch.empty((M, N), dtype=A.dtype, device=A.device)
-    return _C.gemm_layouts(A, B, out, a_is_km, b_is_kn)
+    return _C.gemm_layouts(A, B, out, a_is_km, b_is_kn, alpha, beta)
 
 
 class HostGemm:

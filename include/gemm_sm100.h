@@ -72,6 +72,14 @@ int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, lo
 int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                     int dtype, int a_is_km, int b_is_kn, void* cuda_stream, int* cuda_error_out);
 
+/* C = alpha * op(A) op(B) + beta * C for any of the four layouts of gemm_sm100_gemm.  alpha and
+ * beta are applied in fp32 in the epilogue, before the single rounding to the output type; with
+ * beta != 0 the old C is read (16-bit, same pitch).  K == 0 is only accepted with beta == 0.
+ * No reference counterpart: its epilogue only converts the accumulator (gemm.cuh:368-377). */
+int gemm_sm100_gemm_scaled(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
+                           long ldc, int dtype, int a_is_km, int b_is_kn, float alpha, float beta,
+                           void* cuda_stream, int* cuda_error_out);
+
 /* C = A * B^T stored into `num_outputs` (1..8) output matrices at once: the epilogue issues one
  * TMA store per output for every finished tile.  All outputs share M, N, ldc and dtype; each
  * pointer must be 16-byte aligned and writable from the current device (its own memory, or a
@@ -79,7 +87,7 @@ int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, 
  * building block of the column-sharded multi-GPU GEMM: rank g passes, for every GPU r,
  * `C_r + g * N_shard` with ldc = N_total, and the all-gather of C happens inside the GEMM as
  * stores over NVLink (no staging buffer, no separate collective; the caller still needs a
- * cross-GPU barrier before reading C).  K must be > 0.  Needs no workspace.
+ * cross-GPU barrier before reading C).  K must be > 0 and N a multiple of 8.  Needs no workspace.
  * No reference counterpart: the reference is single-GPU (one store per tile, gemm.cuh:388-394). */
 int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int num_outputs, int M, int N,
                          int K, long lda, long ldb, long ldc, int dtype, void* cuda_stream, int* cuda_error_out);

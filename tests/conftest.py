@@ -50,6 +50,9 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_nn.restype = I
     lib.gemm_sm100_gemm.argtypes = [P, P, P, I, I, I, L, L, L, I, I, I, P, ctypes.POINTER(I)]
     lib.gemm_sm100_gemm.restype = I
+    lib.gemm_sm100_gemm_scaled.argtypes = [P, P, P, I, I, I, L, L, L, I, I, I, ctypes.c_float, ctypes.c_float, P,
+                                           ctypes.POINTER(I)]
+    lib.gemm_sm100_gemm_scaled.restype = I
     lib.gemm_sm100_tn_fanout.argtypes = [P, P, ctypes.POINTER(P), I, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]
     lib.gemm_sm100_tn_fanout.restype = I
     lib.gemm_sm100_tn_static_scratch.argtypes = [P, P, P, I, I, I, L, L, L, I, P, ctypes.POINTER(I)]

@@ -79,6 +79,17 @@ def test_empty_problem_is_a_noop(capi):
     assert capi.gemm_sm100_tn(None, None, None, 8, 0, 8, 8, 8, 8, 0, None, 0, None, ctypes.byref(err)) == 0
 
 
+def test_scaled_entry_validates_on_the_host(capi):
+    err = ctypes.c_int(0)
+    # K == 0 with beta != 0 would be "C *= beta", which is not this library's job.
+    assert capi.gemm_sm100_gemm_scaled(256, 512, 1024, 8, 8, 0, 8, 8, 8, 0, 0, 0, 1.0, 0.5, None,
+                                       ctypes.byref(err)) == 2
+    assert capi.gemm_sm100_gemm_scaled(256, 512, 1024, 8, 8, 12, 16, 16, 8, 0, 0, 0, 2.0, 0.0, None,
+                                       ctypes.byref(err)) == 2
+    assert capi.gemm_sm100_gemm_scaled(None, None, None, 0, 8, 8, 8, 8, 8, 0, 0, 1, 2.0, 1.0, None,
+                                       ctypes.byref(err)) == 0
+
+
 def test_binding_rejects_bad_tensors_with_runtime_error():
     """Shape and dtype checks of the binding need no device: wrong dtype, K mismatch, wrong rank,
     wrong C shape, strided K all raise RuntimeError (the reference's TORCH_CHECKs,

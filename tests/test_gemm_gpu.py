@@ -223,6 +223,28 @@ def test_binding_accepts_row_pitched_operands(gk):
     assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
 
 
+@pytest.mark.parametrize("config", [-1] + list(range(NUM_CONFIGS)))
+@pytest.mark.parametrize("N", [259, 3, 64 + 5, 512 + 7, 1])
+def test_ragged_n_inside_wider_buffer_leaves_neighbours_alone(capi, N, config):
+    """N not a multiple of 8 is only possible for C inside a wider buffer.  The elements right of
+    column N-1 belong to the caller: they must keep their bits (ternary operands: C is exact)."""
+    M, K = 200, 128
+    A, B = oracle.make_ternary_inputs(M, N, K, 54)
+    width = (N + 7) // 8 * 8 + 16
+    wide0 = torch.randn(M, width, generator=torch.Generator().manual_seed(55)).to(torch.bfloat16)
+    wide = wide0.cuda()
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    split = capi.gemm_sm100_set_option(b"split_k", 1) if config in (1, 2) else None
+    assert capi_gemm(capi, A.cuda(), B.cuda(), wide[:, 8:8 + N], ldc=width) == 0
+    if split is not None:
+        capi.gemm_sm100_set_option(b"split_k", -1)
+    assert capi_status(capi) == (0, 0)
+    got = wide.cpu()
+    assert torch.equal(got[:, 8:8 + N].float(), A.float() @ B.float().T)
+    assert torch.equal(got[:, :8].view(torch.int16), wide0[:, :8].view(torch.int16))
+    assert torch.equal(got[:, 8 + N:].view(torch.int16), wide0[:, 8 + N:].view(torch.int16))
+
+
 @pytest.mark.parametrize("shape,panels", [((1024, 768, 320), 4), ((300, 264, 72), 8), ((2048, 512, 256), 3)])
 def test_host_memory_entry_point(gk, shape, panels):
     M, N, K = shape
@@ -394,6 +416,88 @@ def test_transposed_a_exact_one_hot(gk):
     C = gk.gemm(A.T.contiguous().cuda(), B.cuda(), a_is_km=True, b_is_kn=True)
     gk.device_status()
     assert torch.equal(C.cpu().view(torch.int16), B[ks].contiguous().view(torch.int16))
+
+
+LAYOUTS = [(False, False), (False, True), (True, False), (True, True)]
+
+
+def _lay(A, Bt, a_is_km, b_is_kn):
+    return (A.T.contiguous().cuda() if a_is_km else A.cuda()), (Bt.T.contiguous().cuda() if b_is_kn else Bt.cuda())
+
+
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3])
+@pytest.mark.parametrize("a_is_km,b_is_kn", LAYOUTS)
+@pytest.mark.parametrize("shape,dtype", [((256, 256, 64), torch.bfloat16), ((304, 520, 72), torch.bfloat16),
+                                         ((512, 768, 320), torch.float16), ((40, 1000, 136), torch.bfloat16)])
+def test_alpha_beta_matches_oracle(gk, capi, shape, dtype, a_is_km, b_is_kn, config):
+    """C = alpha * op(A) op(B) + beta * C0 against alpha * oracle + beta * C0 in fp32, every layout,
+    ragged edges included (the old C is read in 16-byte pieces clipped at N)."""
+    M, N, K = shape
+    alpha, beta = 0.75, -1.5
+    A, Bt = oracle.make_inputs(M, N, K, 130, dtype)
+    C0 = (torch.randn(M, N, generator=torch.Generator().manual_seed(131)) * 0.5).to(dtype)
+    Ain, Bin = _lay(A, Bt, a_is_km, b_is_kn)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    C = C0.cuda()
+    gk.gemm(Ain, Bin, C, a_is_km=a_is_km, b_is_kn=b_is_kn, alpha=alpha, beta=beta)
+    gk.device_status()
+    want = alpha * oracle.c_gemm_tn_f32(A, Bt) + beta * C0.float()
+    assert_close(C.cpu(), want, dtype)
+
+
+@pytest.mark.parametrize("a_is_km,b_is_kn", LAYOUTS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_alpha_beta_exact_on_integers(gk, dtype, a_is_km, b_is_kn):
+    """Ternary operands, small-integer C0, alpha = 0.5 and beta = 2: every value is exact in fp32
+    and in the output type, so the result must match the integer arithmetic bit for bit."""
+    M, N, K = 264, 328, 128
+    A, Bt = oracle.make_ternary_inputs(M, N, K, 132, dtype)
+    C0 = torch.randint(-8, 9, (M, N), generator=torch.Generator().manual_seed(133)).to(dtype)
+    Ain, Bin = _lay(A, Bt, a_is_km, b_is_kn)
+    C = C0.cuda()
+    gk.gemm(Ain, Bin, C, a_is_km=a_is_km, b_is_kn=b_is_kn, alpha=0.5, beta=2.0)
+    gk.device_status()
+    want = 0.5 * (A.double() @ Bt.double().T) + 2.0 * C0.double()
+    assert torch.equal(C.cpu().double(), want)
+
+
+def test_beta_one_on_zero_c_equals_plain_gemm(gk):
+    """beta = 1 over a zeroed C goes through the scaled epilogue and must reproduce the plain TN
+    kernel's values exactly (same accumulator, one rounding)."""
+    M, N, K = 512, 640, 1024
+    A, Bt = oracle.make_inputs(M, N, K, 134)
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm(A.cuda(), Bt.cuda(), C, b_is_kn=False, alpha=1.0, beta=1.0)
+    C_tn = torch.empty_like(C)
+    gk.gemm_tn_test(A.cuda(), Bt.cuda(), C_tn)
+    gk.device_status()
+    assert torch.equal(C.float(), C_tn.float())
+
+
+def test_alpha_only_leaves_c_unread(gk):
+    """beta == 0 must not read C: NaNs in the old C may not leak into the result."""
+    M, N, K = 256, 384, 256
+    A, Bt = oracle.make_inputs(M, N, K, 135)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gk.gemm(A.cuda(), Bt.cuda(), C, b_is_kn=False, alpha=2.0)
+    gk.device_status()
+    assert_close(C.cpu(), 2.0 * oracle.c_gemm_tn_f32(A, Bt), torch.bfloat16)
+
+
+def test_accumulate_into_row_pitched_c(gk):
+    """C as a column window of a wider buffer: old values are read with the window's pitch and the
+    columns outside it stay untouched."""
+    M, N, K = 200, 259, 192                      # N % 8 != 0: the last piece of old C is read by element
+    A, Bt = oracle.make_inputs(M, N, K, 136)
+    wide0 = (torch.randn(M, N + 61, generator=torch.Generator().manual_seed(137))).to(torch.bfloat16)
+    wide = wide0.cuda()
+    C = wide[:, 24:24 + N]
+    gk.gemm(A.cuda(), Bt.cuda(), C, b_is_kn=False, alpha=1.0, beta=1.0)
+    gk.device_status()
+    want = oracle.c_gemm_tn_f32(A, Bt) + wide0[:, 24:24 + N].float()
+    assert_close(wide[:, 24:24 + N].cpu(), want, torch.bfloat16)
+    assert torch.equal(wide[:, :24].cpu().view(torch.int16), wide0[:, :24].view(torch.int16))
+    assert torch.equal(wide[:, 24 + N:].cpu().view(torch.int16), wide0[:, 24 + N:].view(torch.int16))
 
 
 def test_nn_layout_row_pitched_b_and_one_hot(gk):
