@@ -441,6 +441,12 @@ def run_multi(args):
     ms = t.item() / args.steps
     tflops = gemm_flops(M, N, K) / ms / 1e9
 
+    def per_rank(total_ms):
+        mine = torch.tensor([total_ms / args.steps], dtype=torch.float64, device=device)
+        every = torch.zeros(world, dtype=torch.float64, device=device)
+        dist.all_gather_into_tensor(every, mine)
+        return [round(x, 4) for x in every.tolist()]
+
     # this rank's GEMM alone (no exchange), same number of steps: shows what the exchange costs
     C_slab = torch.empty((M, hi - lo), dtype=dtype, device=device)
     local_step = lambda: gk.gemm_tn_test(A, B_shard, C_slab)  # noqa: E731
@@ -449,6 +455,7 @@ def run_multi(args):
     t = torch.tensor([local_total], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     local_ms = t.item() / args.steps
+    local_ms_per_rank = per_rank(local_total)
     del C_slab
 
     # end to end: operands start in pinned host memory, the result ends there, every step.  The
@@ -488,6 +495,9 @@ def run_multi(args):
                        "per_gpu_tflops": round(per_gpu, 2),
                        "local_gemm_ms_per_step": round(local_ms, 4),
                        "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange",
+                       "local_gemm_ms_per_rank": local_ms_per_rank,
+                       "local_gemm_per_rank_note": "the GPUs of a box differ under the power cap; a step that "
+                                                   "ends in a cross-GPU barrier runs at the slowest one's pace",
                        "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"},
             "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,
