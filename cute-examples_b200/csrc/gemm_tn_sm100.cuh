@@ -176,10 +176,16 @@ struct WorkIter {
       return true;
     } else {
       if (u >= u_end) return false;
-      s.tile = (int)(u / k_blocks);
-      s.kb0 = (int)(u - (long long)s.tile * k_blocks);
+      int tile_ = (int)(u / k_blocks);
+      int kb0_ = (int)(u - (long long)tile_ * k_blocks);
       const long long left = u_end - u;
-      s.kb1 = (left < (long long)(k_blocks - s.kb0)) ? s.kb0 + (int)left : k_blocks;
+      int kb1_ = (left < (long long)(k_blocks - kb0_)) ? kb0_ + (int)left : k_blocks;
+      // Every lane holds the same values, but they come out of a 64-bit division in the vector
+      // datapath; a warp reduction hands them back as warp-uniform values, which the loops built
+      // on them (barrier waits, TMA and MMA issue) need to stay in uniform registers.
+      s.tile = __reduce_max_sync(0xffffffffu, tile_);
+      s.kb0 = __reduce_max_sync(0xffffffffu, kb0_);
+      s.kb1 = __reduce_max_sync(0xffffffffu, kb1_);
       u += s.kb1 - s.kb0;
       return true;
     }
