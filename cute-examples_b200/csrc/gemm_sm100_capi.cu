@@ -195,12 +195,16 @@ int validate(const Problem& p) {
 
 inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 
-// Cost model used to choose a tile configuration: time ~ waves x (per-CTA work of one tile) /
-// (relative rate of the configuration), where a wave is one tile on every resident CTA (pair).
-// Rates are measured on B200 at 8192^3 (power-capped steady state), relative to the 256 x 512
-// pair tile: the wider the tile, the fewer bytes cross L2 -> shared memory per flop.
+// Cost model used to choose a tile configuration: time ~ waves x (K blocks of a tile + what a tile
+// boundary costs) x tile columns / (relative rate of the configuration), where a wave is one tile
+// on every resident CTA (pair).  Fitted to interleaved timings of the configurations on B200
+// (power-capped steady state; 8192^3, 8192 x 8192 x {2048, 4096}, the two MLP shapes): the two pair
+// tiles run at the same rate within 1 %, and the 256 x 512 tile, whose accumulator fills TMEM,
+// loses about one K block per tile because its next tile cannot start before the accumulator is
+// drained.  So short K and bad wave counts go to the 256 x 256 tile, the rest to the wider one.
 constexpr int kAutoConfigs = 4;                       // candidates of the automatic choice
-constexpr double kConfigRate[kAutoConfigs] = {0.96, 1.0, 0.72, 0.5};
+constexpr double kConfigRate[kAutoConfigs] = {0.99, 1.0, 0.72, 0.5};
+constexpr double kTileBoundaryKBlocks[kAutoConfigs] = {0.0, 1.0, 0.0, 0.0};
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
 constexpr bool has_split_k(int config) { return config == 1 || config == 2; }
@@ -241,7 +245,8 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true) {
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
     // costs in units of (one K block of one tile column) per CTA
-    double cost = static_cast<double>(waves) * block_n * k_blocks / rate;
+    const double boundary = i < kAutoConfigs ? kTileBoundaryKBlocks[i] : 0.0;
+    double cost = static_cast<double>(waves) * block_n * (k_blocks + boundary) / rate;
     const long units = tiles * k_blocks;
     const long ranges = units < slots ? units : slots;
     // K-split: every CTA (pair) gets units / ranges K blocks, plus the fix-up of the cut tiles
@@ -645,8 +650,11 @@ int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int
   Problem p{A, B, outputs[0], M, N, K, lda, ldb, ldc, dtype};
   // Pair-tile configurations only; the same wave model as the plain GEMM picks between them.
   const long slots = st->sm_count / 2;
-  const double cost0 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 256L), slots)) * 256 / kConfigRate[0];
-  const double cost1 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 512L), slots)) * 512 / kConfigRate[1];
+  const double k_blocks = static_cast<double>(ceil_div(K, 64L));
+  const double cost0 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 256L), slots)) * 256 *
+                       (k_blocks + kTileBoundaryKBlocks[0]) / kConfigRate[0];
+  const double cost1 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 512L), slots)) * 512 *
+                       (k_blocks + kTileBoundaryKBlocks[1]) / kConfigRate[1];
   const bool wide = g_opt_tile_config == 1 || (g_opt_tile_config != 0 && cost1 <= cost0);
   if (dtype == GEMM_SM100_BF16)
     return wide ? launch_fanout<1, true>(p, outputs, num_outputs, *st, stream, cuda_error_out)
