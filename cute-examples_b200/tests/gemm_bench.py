@@ -3,8 +3,9 @@
 Successor of the part of the reference's kernels/tests/gemm_bench.py that times its own kernel
 and torch.mm (benchmark_gemm_custom :278-295, benchmark_comparison :451-585,
 profile_different_shapes :610-706).  Differences: CUDA-event timing on the stream instead of
-perf_counter around a synchronised call, operands created once per shape, L2 flushed between
-iterations by writing a 512 MiB scratch buffer (the reference allocates an 80 MB tensor per run,
+perf_counter around a synchronised call, the two implementations timed in alternation (10 warm-up
+and 30 timed iterations each; the speed-up is the median of the per-iteration ratios), operands
+created once per shape, L2 flushed between iterations by writing a 512 MiB scratch buffer (the reference allocates an 80 MB tensor per run,
 :58-61), a B200 entry in the peak table (:592-599 has none), and one JSON line per shape.
 Its ctypes-cuBLAS autotuner (:124-276) is not reproduced.
 """
@@ -38,20 +39,26 @@ def peak_for_device():
     return name, None
 
 
-def time_fn(fn, scratch, warmup=3, iters=10):
+def time_pair(ours, theirs, scratch, warmup=10, iters=30):
+    """Times the two callables in alternation (flush, ours, flush, theirs, ...): under the power cap
+    the clock drifts within seconds, and timing one after the other would charge the drift to one
+    of them.  Returns (median, min) of each and the median of the per-iteration time ratios."""
     for _ in range(warmup):
-        fn()
+        ours()
+        theirs()
     torch.cuda.synchronize()
-    times = []
+    t_ours, t_theirs = [], []
     for _ in range(iters):
-        scratch.add_(1)                                     # evict operands from L2
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        fn()
-        e.record()
-        e.synchronize()
-        times.append(s.elapsed_time(e))
-    return statistics.median(times), min(times)
+        for fn, times in ((ours, t_ours), (theirs, t_theirs)):
+            scratch.add_(1)                                 # evict operands from L2
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            e.synchronize()
+            times.append(s.elapsed_time(e))
+    ratio = statistics.median(b / a for a, b in zip(t_ours, t_theirs))
+    return (statistics.median(t_ours), min(t_ours)), (statistics.median(t_theirs), min(t_theirs)), ratio
 
 
 def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
@@ -60,21 +67,21 @@ def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     C2 = torch.empty((M, N), device="cuda", dtype=dtype)
     if layout == "tn":
         B = (torch.randn((N, K), device="cuda") / K ** 0.5).to(dtype)    # already [N, K]: no transpose copy
-        ours_med, ours_min = time_fn(lambda: gk.gemm_tn_test(A, B, C), scratch)
+        (ours_med, ours_min), (torch_med, torch_min), ratio = time_pair(
+            lambda: gk.gemm_tn_test(A, B, C), lambda: torch.mm(A, B.T, out=C2), scratch)
         gk.device_status()
-        torch_med, torch_min = time_fn(lambda: torch.mm(A, B.T, out=C2), scratch)
     else:
         B = (torch.randn((K, N), device="cuda") / K ** 0.5).to(dtype)    # [K, N], as torch.mm takes it
-        ours_med, ours_min = time_fn(lambda: gk.gemm_nn(A, B, C), scratch)
+        (ours_med, ours_min), (torch_med, torch_min), ratio = time_pair(
+            lambda: gk.gemm_nn(A, B, C), lambda: torch.mm(A, B, out=C2), scratch)
         gk.device_status()
-        torch_med, torch_min = time_fn(lambda: torch.mm(A, B, out=C2), scratch)
     flops = 2.0 * M * N * K
     nbytes = 2.0 * (M * K + N * K + M * N)
     rec = {
         "M": M, "N": N, "K": K, "dtype": str(dtype).replace("torch.", ""), "layout": layout,
         "ours_ms": round(ours_med, 4), "ours_min_ms": round(ours_min, 4), "torch_ms": round(torch_med, 4),
         "ours_tflops": round(flops / ours_med / 1e9, 1), "torch_tflops": round(flops / torch_med / 1e9, 1),
-        "speedup_vs_torch": round(torch_med / ours_med, 3), "ours_gbs": round(nbytes / ours_med / 1e6, 1),
+        "torch_min_ms": round(torch_min, 4), "speedup_vs_torch": round(ratio, 3), "ours_gbs": round(nbytes / ours_med / 1e6, 1),
         "tile_config": gk.describe_config(gk.select_config(M, N, K, gk.DTYPE_CODES[dtype])),
         "max_abs_diff_vs_torch": float((C.float() - C2.float()).abs().max().item()),
     }
