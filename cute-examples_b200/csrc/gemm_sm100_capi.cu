@@ -9,6 +9,7 @@
 // :82-85 -> cudaLaunchKernelEx on the caller's stream;  sync + exit on error :86 ->
 // asynchronous, errors returned.
 #include <cuda.h>
+#include <cmath>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -248,16 +249,37 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true) {
     const double boundary = i < kAutoConfigs ? kTileBoundaryKBlocks[i] : 0.0;
     double cost = static_cast<double>(waves) * block_n * (k_blocks + boundary) / rate;
     const long units = tiles * k_blocks;
-    const long ranges = units < slots ? units : slots;
-    // K-split: every CTA (pair) gets units / ranges K blocks, plus the fix-up of the cut tiles
-    // (partial tile out and in, a wait for the neighbour: about 9 K blocks' worth of time).
-    const double split_cost = static_cast<double>(units) / ranges * block_n / rate + 9.0 * block_n;
-    // Automatic choice: only when whole tiles would leave more than half of the SMs idle and every
-    // CTA still gets a long run of K blocks.  (Measured on B200: for 4096^3, 1.73 waves of
-    // 256 x 512 tiles, the K-split schedule took 111 us against 95 us for whole tiles: the three
-    // exposed epilogues per CTA pair and the lost lockstep sharing of operands cost more than the
-    // idle quarter wave.  So a bad wave count alone does not select it.)
-    const bool auto_split = g_opt_split_k < 0 && units >= slots * 16 && tiles * 2 <= slots;
+    // K-split.  Forced (split_k = 1): as many ranges as CTA (pair)s.  Automatic: the 128 x 256
+    // tile only, when whole tiles would leave more than half of the SMs idle, with the number of
+    // ranges that minimises   K blocks per range / rate + 7 x ranges per tile + 20   (in K blocks
+    // of this tile).  The terms, fitted to timings of 128..1024 x 256..4096 x 4096..65536 on B200:
+    // the owner of a cut tile sums its contributors' fp32 partial tiles alone (about 7 K blocks'
+    // worth of time each), and a cut launch costs about 20 K blocks more than a whole one (counters
+    // zeroed by a memset node, partial tiles written, accumulator drains).  CTAs that work on the
+    // same operand panel at different K offsets no longer fetch it together, so operands beyond
+    // what L2 holds are charged as DRAM traffic (2048 x 2048 x 8192 with the 256 x 512 tile: 92 us
+    // cut against 53 us whole).  For 4096^3 (1.73 waves) cutting took 111 us against 95 us: a bad
+    // wave count alone never selects it.
+    const bool forced_split = g_opt_split_k > 0;
+    long ranges = units < slots ? units : slots;
+    double split_cost = static_cast<double>(units) / ranges * block_n / rate + 9.0 * block_n;
+    bool auto_split = false;
+    if (!forced_split && g_opt_split_k < 0 && i == kSplitKConfig && tiles * 2 <= slots) {
+      long r = static_cast<long>(std::sqrt(static_cast<double>(units) * tiles / 5.0) + 0.5);
+      if (r > slots) r = slots;
+      if (r > units / 4) r = units / 4;                      // at least four K blocks per range
+      if (r >= 2 * tiles) {
+        const double operand_bytes = 2.0 * (static_cast<double>(M) + N) * K;
+        const double miss = operand_bytes > 48e6 ? 1.0 - 48e6 / operand_bytes : 0.0;
+        double stream = static_cast<double>(units) / r / rate;
+        const double dram = static_cast<double>(units) * 0.0204 * miss;
+        if (dram > stream) stream = dram;
+        ranges = r;
+        split_cost = (stream + 7.0 * r / tiles + 20.0) * block_n;
+        auto_split = split_cost < cost;
+        split_cost *= 1.15;                                  // the fit is good to about 10 %: ties go to whole tiles
+      }
+    }
     const bool can_split = allow_split && has_split_k(i) && units >= 2;
     if (can_split && (g_opt_split_k > 0 || auto_split)) {
       cost = split_cost;
