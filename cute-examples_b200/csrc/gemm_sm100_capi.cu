@@ -89,7 +89,7 @@ struct EnvOverrides {
   }
   EnvOverrides() {
     read("GEMM_SM100_TILE_CONFIG", g_opt_tile_config, -1, kNumConfigs - 1);
-    read("GEMM_SM100_SPLIT_K", g_opt_split_k, -1, 1);
+    read("GEMM_SM100_SPLIT_K", g_opt_split_k, -1, 8);
     read("GEMM_SM100_GROUP_M", g_opt_group_m, 0, 4096);
     read("GEMM_SM100_MAX_CTAS", g_opt_max_ctas, 0, 1 << 20);
     read("GEMM_SM100_TIMEOUT_MS", g_opt_timeout_ms, 1, 60000);
@@ -208,7 +208,14 @@ constexpr double kConfigRate[kAutoConfigs] = {0.99, 1.0, 0.72, 0.5};
 constexpr double kTileBoundaryKBlocks[kAutoConfigs] = {0.0, 1.0, 0.0, 0.0};
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
-constexpr bool has_split_k(int config) { return config == 1 || config == 2; }
+constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2; }
+// Configurations whose K-split kernel also has the even split (single-width tiles).
+constexpr bool has_even_split(int config) { return config == 0 || config == 2; }
+// Even split: what cutting costs per wave of units on top of the K blocks, in K blocks of the
+// configuration's tile: about 12 us measured on B200 (counters zeroed by a memset node, partial
+// tiles written, the wait for the other contributors, one tile's worth of partial data read back
+// and stored; little of it overlaps the next unit's main loop).
+constexpr double kEvenSplitFixupKBlocks[kAutoConfigs] = {43.0, 0.0, 32.0, 0.0};
 
 struct Plan {
   int config = 0;
@@ -217,6 +224,7 @@ struct Plan {
   size_t flag_bytes = 0;     // K-split: arrival counters (one per CTA), padded to 256 bytes
   size_t partial_bytes = 0;  // K-split: one fp32 partial tile per CTA
   int partial_rows = 128;    // K-split: rows kept per partial tile
+  int split_factor = 0;      // K-split: > 1 = every tile cut into this many equal K ranges
 };
 
 inline int grid_cap(const ConfigInfo& c, int sm_count) {
@@ -281,7 +289,33 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true) {
       }
     }
     const bool can_split = allow_split && has_split_k(i) && units >= 2;
-    if (can_split && (g_opt_split_k > 0 || auto_split)) {
+    // Even split: every tile cut into s equal K ranges, the reduction spread over the contributors.
+    // Forced with split_k = s (2..8); automatic when it beats whole tiles and the contiguous ranges.
+    int even_s = 0;
+    double even_cost = 1e300;
+    if (allow_split && has_even_split(i) && g_opt_split_k != 0 && g_opt_split_k != 1) {
+      for (int f = 2; f <= 8; ++f) {
+        if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
+        if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
+        const double c_f = static_cast<double>(ceil_div(tiles * f, slots)) *
+                           (static_cast<double>(k_blocks) / f + boundary + kEvenSplitFixupKBlocks[i]) * block_n / rate;
+        if (c_f < even_cost) {
+          even_cost = c_f;
+          even_s = f;
+        }
+      }
+    }
+    const double best_other = (can_split && auto_split) ? split_cost : cost;
+    if (even_s > 0 && (g_opt_split_k > 1 || even_cost < best_other)) {
+      const long even_units = tiles * even_s;
+      cost = even_cost * 1.1;                                // ties go to the simpler schedule
+      cand.split_k = true;
+      cand.split_factor = even_s;
+      cand.ctas = static_cast<int>((even_units < slots ? even_units : slots) * c.cta_group);
+      cand.partial_rows = M < 128 ? static_cast<int>((M + 31) / 32 * 32) : 128;
+      cand.flag_bytes = (static_cast<size_t>(tiles) * c.cta_group * sizeof(unsigned int) + 255) / 256 * 256;
+      cand.partial_bytes = static_cast<size_t>(even_units) * c.cta_group * cand.partial_rows * block_n * sizeof(float);
+    } else if (can_split && (g_opt_split_k == 1 || auto_split)) {
       cost = split_cost;
       cand.split_k = true;
       cand.ctas = static_cast<int>(ranges * c.cta_group);
@@ -318,6 +352,7 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.sk_flags = nullptr;
   tp.sk_partials = nullptr;
   tp.sk_rows = 128;
+  tp.sk_factor = 0;
   tp.k_rotate = 0;
   tp.alpha = p.alpha;
   tp.beta = p.beta;
@@ -384,6 +419,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
     tp.sk_flags = static_cast<unsigned int*>(workspace);
     tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
     tp.sk_rows = plan.partial_rows;
+    tp.sk_factor = plan.split_factor;
     e = cudaMemsetAsync(tp.sk_flags, 0, plan.flag_bytes, stream);
     if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   }
@@ -810,7 +846,7 @@ int gemm_sm100_set_option(const char* name, long value) {
     return GEMM_SM100_OK;
   }
   if (std::strcmp(name, "split_k") == 0) {
-    if (value < -1 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    if (value < -1 || value > 8) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_split_k = value;
     return GEMM_SM100_OK;
   }

@@ -67,6 +67,8 @@ struct TileParams {
   unsigned int* sk_flags;          // zeroed before the launch
   float* sk_partials;              // grid x (sk_rows x kBlockN) floats
   int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
+  int sk_factor;                   // <= 1: contiguous ranges; > 1: every tile cut into this many equal K ranges
+                                   // (then one partial tile per unit and CTA of the pair, one counter per tile and CTA)
   // Start every tile's K loop at a different K block (wrapping around).  Used when each B tile is
   // read exactly once (a single tile row, the memory-bound small-M case): the CTAs then stream
   // different column offsets at any moment, which spreads the requests over the DRAM channels.
@@ -144,6 +146,7 @@ struct GemmConfig {
 // A run of consecutive K blocks of one output tile.
 struct Segment {
   int tile, kb0, kb1;
+  int part;   // even split only: which of the tile's `factor` equal K ranges this is
 };
 
 // What one CTA (pair) works on, as a sequence of segments.
@@ -152,16 +155,21 @@ struct Segment {
 //    one per CTA (pair), so every SM streams the same number of K blocks whatever the tile
 //    count; a tile cut by a range boundary is summed by the owner of its first K block from
 //    fp32 partial tiles the other owners leave in global memory.
+//  kSplitK == true with factor > 1 ("even split", single-width tiles): every tile is cut into
+//    `factor` equal K ranges, range j of tile t is unit t * factor + j, units go round-robin over
+//    the CTA (pair)s; every contributor writes an fp32 partial tile and then, once the tile's
+//    arrival counter is full, reduces and stores its own share of the tile, so the reduction is
+//    spread over the contributors instead of falling to one owner.
 template <bool kSplitK>
 struct WorkIter {
-  int tile, step, num_tiles, k_blocks;
+  int tile, step, num_tiles, k_blocks, factor;
   long long u, u_end;
 
   __device__ __forceinline__ static long long range_start(int cluster, int clusters, long long units) {
     return (long long)cluster * units / clusters;
   }
-  __device__ __forceinline__ WorkIter(int cluster, int clusters, int num_tiles_, int k_blocks_)
-      : tile(cluster), step(clusters), num_tiles(num_tiles_), k_blocks(k_blocks_) {
+  __device__ __forceinline__ WorkIter(int cluster, int clusters, int num_tiles_, int k_blocks_, int factor_ = 0)
+      : tile(cluster), step(clusters), num_tiles(num_tiles_), k_blocks(k_blocks_), factor(factor_) {
     const long long units = (long long)num_tiles_ * k_blocks_;
     u = range_start(cluster, clusters, units);
     u_end = range_start(cluster + 1, clusters, units);
@@ -175,6 +183,17 @@ struct WorkIter {
       tile += step;
       return true;
     } else {
+      if (factor > 1) {
+        // even split: `tile` walks the units
+        if (tile >= num_tiles * factor) return false;
+        const int t_ = tile / factor, j_ = tile - t_ * factor;
+        s.tile = __reduce_max_sync(0xffffffffu, t_);
+        s.part = __reduce_max_sync(0xffffffffu, j_);
+        s.kb0 = __reduce_max_sync(0xffffffffu, (int)((long long)j_ * k_blocks / factor));
+        s.kb1 = __reduce_max_sync(0xffffffffu, (int)((long long)(j_ + 1) * k_blocks / factor));
+        tile += step;
+        return true;
+      }
       if (u >= u_end) return false;
       int tile_ = (int)(u / k_blocks);
       int kb0_ = (int)(u - (long long)tile_ * k_blocks);
@@ -394,6 +413,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   const int cluster_id = blockIdx.x / G;
   const int num_clusters = gridDim.x / G;
   const int k_blocks = p.k_blocks;
+  const int sk_factor = (kSplitK && Cfg::kHalves == 1) ? p.sk_factor : 0;   // even split: single-width tiles only
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -407,7 +427,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       // thread is the only consumer of the ring.
       const uint32_t full_leader = (G == 2) ? map_to_cta(bar_base + kFullOff, 0u) : bar_base + kFullOff;
       uint32_t phase = 0;
-      WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
+      WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
       Segment seg;
       bool have = work.next(seg);
       int kb = seg.kb0, row_a = 0, row_b = 0, rot = 0;
@@ -496,7 +516,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       constexpr uint32_t kBStepK = kBIsKN ? 128u : 2u;
       const uint32_t bar_peer = (G == 2) ? map_to_cta(bar_base, 1u) : bar_base;
       uint32_t phase = 0;
-      WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
+      WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
       Segment seg;
       bool have = work.next(seg);
       int kb = seg.kb0, iter = 0;          // iter counts segments: it selects the accumulator slot
@@ -606,7 +626,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     uint32_t buf = 0;
     bool ok = true;
     long long stall = 0;
-    WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks);
+    WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
     Segment seg;
     // K-split schedule: 16-byte pieces of a partial tile are laid out [piece][row][4 floats], so
     // the 32 rows a warp owns are 512 contiguous bytes per piece.  Only rows below M exist.
@@ -618,8 +638,13 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       tile_coords(seg.tile, p, m_tile, n_tile);
       const int row0 = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + q * 32;
       const bool row_live = row0 + (int)lane < p.M;          // rows past M hold zeros: never moved
-      const bool writes_partial = kSplitK && seg.kb0 != 0;
-      const bool reduces = kSplitK && seg.kb0 == 0 && seg.kb1 != k_blocks;
+      // Contiguous ranges: a segment that does not start its tile leaves a partial tile for the
+      // tile's owner.  Even split: every contributor leaves one, nobody owns the tile.
+      const bool even = kSplitK && sk_factor > 1;
+      const bool writes_partial = kSplitK && (even || seg.kb0 != 0);
+      const bool reduces = kSplitK && !even && seg.kb0 == 0 && seg.kb1 != k_blocks;
+      // this segment's partial tile: one per CTA, or one per unit and CTA of the pair
+      const size_t my_partial = even ? ((size_t)(seg.tile * sk_factor + seg.part) * G + cta_rank) : (size_t)blockIdx.x;
       int writer_first = 0, writer_count = 0;
       if constexpr (kSplitK) {
         if (reduces) {
@@ -657,7 +682,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             const int piece0 = (h * kChunks + c) * 16;       // first 16-byte piece of this chunk
             if (writes_partial) {
               if (row_live) {
-                float4* dst = reinterpret_cast<float4*>(p.sk_partials + (size_t)blockIdx.x * partial_floats) +
+                float4* dst = reinterpret_cast<float4*>(p.sk_partials + my_partial * partial_floats) +
                               (size_t)piece0 * sk_rows + my_row;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -817,7 +842,69 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           // Publish this warp's share of the partial tile: writes, fence, then one arrival.
           __threadfence();
           __syncwarp();
-          if (lane == 0) atomicAdd(p.sk_flags + blockIdx.x, 1u);
+          if (lane == 0) atomicAdd(p.sk_flags + (even ? (size_t)seg.tile * G + cta_rank : (size_t)blockIdx.x), 1u);
+        }
+        if constexpr (Cfg::kHalves == 1) {
+          if (ok && even) {
+            // Every contributor of the tile has arrived once all their epilogue warps have: then this
+            // one reduces and stores its share, the 32-row x 64-column blocks b with b % factor == part
+            // (dealt round-robin to its warps), adding the partial tiles in range order.  Plain
+            // 16-byte stores from registers: a lane owns 128 contiguous bytes of one row of C.
+            ok = wait_counter(p.sk_flags + (size_t)seg.tile * G + cta_rank, Cfg::kEpiWarps * sk_factor, ctx,
+                              kStatusTimeoutPartial);
+            if (!ok) break;
+            constexpr int kBlocks = 4 * kChunks;                   // 4 row quarters x 64-column chunks
+            int dealt = 0;
+#pragma unroll 1
+            for (int b = seg.part; b < kBlocks; b += sk_factor, ++dealt) {
+              if (dealt % Cfg::kEpiWarps != e) continue;
+              const int bq = b & 3, bc = b >> 2;                  // row quarter, chunk of the tile
+              const int row = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + bq * 32 + (int)lane;
+              const int colc = n_tile * Cfg::kBlockN + bc * Cfg::kEpiCols;
+              if (row >= p.M || colc >= p.N || (kDebug && (dbg & kDebugSkipStores))) continue;
+              uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)row * p.ldc + colc;
+#pragma unroll 1
+              for (int half = 0; half < 2; ++half) {              // 32 columns at a time: eight loads in flight
+                float4 acc[8];
+#pragma unroll 1
+                for (int i = 0; i < sk_factor; ++i) {
+                  const float4* src = reinterpret_cast<const float4*>(
+                                          p.sk_partials + ((size_t)(seg.tile * sk_factor + i) * G + cta_rank) * partial_floats) +
+                                      (size_t)(bc * 16 + half * 8) * sk_rows + bq * 32 + lane;
+                  float4 t[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) t[j] = __ldcg(src + (size_t)j * sk_rows);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    if (i == 0) {
+                      acc[j] = t[j];
+                    } else {
+                      acc[j].x += t[j].x;
+                      acc[j].y += t[j].y;
+                      acc[j].z += t[j].z;
+                      acc[j].w += t[j].w;
+                    }
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {                     // 8 columns = 16 bytes of C per step
+                  const int col = colc + half * 32 + j * 8;
+                  const uint32_t w0 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].x), __float_as_uint(acc[2 * j].y));
+                  const uint32_t w1 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].z), __float_as_uint(acc[2 * j].w));
+                  const uint32_t w2 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j + 1].x), __float_as_uint(acc[2 * j + 1].y));
+                  const uint32_t w3 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j + 1].z), __float_as_uint(acc[2 * j + 1].w));
+                  if (col + 8 <= p.N) {
+                    *reinterpret_cast<uint4*>(crow + half * 32 + j * 8) = make_uint4(w0, w1, w2, w3);
+                  } else {
+                    const uint32_t w[4] = {w0, w1, w2, w3};
+#pragma unroll
+                    for (int t2 = 0; t2 < 8; ++t2)
+                      if (col + t2 < p.N) crow[half * 32 + j * 8 + t2] = (uint16_t)(w[t2 >> 1] >> (16 * (t2 & 1)));
+                  }
+                }
+              }
+            }
+          }
         }
       }
     }

@@ -143,8 +143,9 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
 /* Tuning / test knobs, process-wide.  Names: "tile_config" (-1 = choose automatically,
  * otherwise an index reported by gemm_sm100_describe_config), "timeout_ms" (bound of each
  * device-side wait, default 2000), "max_ctas" (0 = all SMs; caps the persistent grid),
- * "split_k" (-1 = automatic, 0 = never, 1 = whenever the chosen configuration has a K-split
- * variant), "group_m" (0 = default; tile rows per rasterisation group), "k_rotate" (0 = off, the default; 1 = on; -1 = on for a single tile row:
+ * "split_k" (-1 = automatic, 0 = never, 1 = contiguous K ranges, one per CTA or pair, whenever the
+ * chosen configuration has a K-split variant; 2..8 = every tile cut into that many equal K ranges
+ * with the reduction spread over the contributors, on the 256 x 256 and 128 x 256 tiles), "group_m" (0 = default; tile rows per rasterisation group), "k_rotate" (0 = off, the default; 1 = on; -1 = on for a single tile row:
  * start each tile's K loop at a different K block).  Set them before
  * asking gemm_sm100_workspace_bytes, which depends on them.  The environment variables
  * GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M, GEMM_SM100_MAX_CTAS and

@@ -336,6 +336,62 @@ def test_split_k_exact_on_integers(capi, dtype, config):
     assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
 
 
+EVEN_SHAPES = [
+    # M, N, K, max_ctas
+    (512, 1024, 4096, 0), (1024, 1024, 2048, 0), (128, 2048, 8192, 0), (300, 1000, 4104, 0),
+    (64, 512, 16384, 0), (768, 768, 2048, 12), (512, 2048, 2560, 8), (1000, 1900 + 4, 2048, 0),
+]
+
+
+@pytest.mark.parametrize("shape", EVEN_SHAPES)
+@pytest.mark.parametrize("factor", [2, 3, 4])
+@pytest.mark.parametrize("config", [0, 2])
+def test_even_split_matches_oracle(capi, shape, factor, config):
+    """Every tile cut into `factor` equal K ranges, partial tiles summed in range order by the
+    contributors themselves: inside the tolerance, same bits on every run, nothing left unwritten."""
+    M, N, K, max_ctas = shape
+    A, B = oracle.make_inputs(M, N, K, 160 + M % 7)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"split_k", factor)
+    capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
+    assert capi.gemm_sm100_workspace_bytes(M, N, K, 0) > 0
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    for _ in range(2):
+        assert torch.equal(C.view(torch.int16), run_capi(capi, A, B).view(torch.int16))
+
+
+@pytest.mark.parametrize("config", [0, 2])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_even_split_exact_on_integers(capi, dtype, config):
+    M, N, K = 384, 1288, 2048           # N % 8 == 0 but not a multiple of 64: ragged last chunk
+    A, B = oracle.make_ternary_inputs(M, N, 256, 161, dtype)
+    A = torch.cat([A, torch.zeros(M, K - 256, dtype=dtype)], dim=1)      # long K, exact sums
+    B = torch.cat([B, torch.zeros(N, K - 256, dtype=dtype)], dim=1)
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"split_k", 4)
+    C = run_capi(capi, A, B)
+    assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
+
+
+def test_even_split_ragged_n_inside_wider_buffer(capi):
+    M, N, K = 200, 259, 2048
+    A, B = oracle.make_ternary_inputs(M, N, 128, 162)
+    A = torch.cat([A, torch.zeros(M, K - 128, dtype=A.dtype)], dim=1)
+    B = torch.cat([B, torch.zeros(N, K - 128, dtype=B.dtype)], dim=1)
+    width = 264 + 16
+    wide0 = torch.randn(M, width, generator=torch.Generator().manual_seed(163)).to(torch.bfloat16)
+    wide = wide0.cuda()
+    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"split_k", 2)
+    assert capi_gemm(capi, A.cuda(), B.cuda(), wide[:, 8:8 + N], ldc=width) == 0
+    assert capi_status(capi) == (0, 0)
+    got = wide.cpu()
+    assert torch.equal(got[:, 8:8 + N].float(), A.float() @ B.float().T)
+    assert torch.equal(got[:, :8].view(torch.int16), wide0[:, :8].view(torch.int16))
+    assert torch.equal(got[:, 8 + N:].view(torch.int16), wide0[:, 8 + N:].view(torch.int16))
+
+
 def test_split_k_rejects_missing_workspace(capi):
     M, N, K = 128, 2048, 4096
     capi.gemm_sm100_set_option(b"tile_config", 2)
