@@ -619,11 +619,15 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
     rc = get_encoder(cuda_error_out);
     if (rc != GEMM_SM100_OK) return rc;
   }
-  const Plan plan = make_plan(M, N, K, st->sm_count);
+  Plan plan = make_plan(M, N, K, st->sm_count);
   if (plan.split_k) {
     if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
-        workspace_bytes < plan.flag_bytes + plan.partial_bytes)
-      return GEMM_SM100_ERR_WORKSPACE;
+        workspace_bytes < plan.flag_bytes + plan.partial_bytes) {
+      // A K-split the caller asked for needs its workspace; one the planner chose by itself is
+      // only an optimisation: without the memory the problem runs as whole tiles.
+      if (g_opt_split_k > 0) return GEMM_SM100_ERR_WORKSPACE;
+      plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false);
+    }
   }
   if (dtype == GEMM_SM100_BF16) return dispatch<true>(plan, p, workspace, *st, stream, cuda_error_out);
   return dispatch<false>(plan, p, workspace, *st, stream, cuda_error_out);

@@ -45,8 +45,10 @@ extern "C" {
  * Requirements: K % 8 == 0, lda/ldb/ldc % 8 == 0, all three base pointers 16-byte aligned,
  * lda, ldb >= K, ldc >= N.  M and N are arbitrary (the reference requires M % 256 == 0,
  * N % 256 == 0, K % 64 == 0: gemm_test.cu:32-41).  M == 0 or N == 0 is a no-op; K == 0 zero-fills C.
- * `workspace` must hold gemm_sm100_workspace_bytes(M, N, K, dtype) bytes (256-byte aligned)
- * when that is non-zero; it may be NULL otherwise.
+ * `workspace` should hold gemm_sm100_workspace_bytes(M, N, K, dtype) bytes (256-byte aligned)
+ * when that is non-zero; it may be NULL otherwise.  Without it a K-split schedule that the
+ * library chose by itself falls back to whole tiles (slower for few-tile, long-K problems); one
+ * forced through the "split_k" option returns GEMM_SM100_ERR_WORKSPACE.
  * Replaces: test::gemm_tn_test, gemm_test.cu:12-92 (argument checks :15-41, tensor-map
  * construction :56-68, launch :70-85).  Differences by design: asynchronous on the caller's
  * stream (the reference uses the legacy default stream and then cudaDeviceSynchronize, :82-86).

@@ -405,6 +405,21 @@ def test_split_k_rejects_missing_workspace(capi):
     assert rc == 7          # GEMM_SM100_ERR_WORKSPACE, nothing launched
 
 
+def test_automatic_split_without_workspace_runs_whole_tiles(capi):
+    """A K-split the planner chose by itself is only an optimisation: a caller that passes no
+    workspace still gets the product (as whole tiles)."""
+    M, N, K = 256, 512, 16384
+    assert capi.gemm_sm100_workspace_bytes(M, N, K, 0) > 0
+    A, B = oracle.make_inputs(M, N, K, 170)
+    Ad, Bd = A.cuda(), B.cuda()
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = ctypes.c_int(0)
+    rc = capi.gemm_sm100_tn(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0, None, 0, None,
+                            ctypes.byref(err))
+    assert rc == 0 and capi_status(capi) == (0, 0)
+    assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
 # --------------------------------------------------------------- B as [K, N]
 NN_SHAPES = [(256, 256, 64), (512, 768, 320), (300, 520, 72), (1024, 1024, 1024), (128, 4096, 512), (100, 264, 2056)]
 
