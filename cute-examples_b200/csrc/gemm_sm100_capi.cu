@@ -35,7 +35,7 @@ constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 7;
+constexpr int kNumConfigs = 8;
 
 struct ConfigInfo {
   int cta_group, mma_n, halves, stages, epi_warps;
@@ -48,6 +48,7 @@ constexpr ConfigInfo kConfigs[kNumConfigs] = {
     {2, 256, 2, 4, 4},
     {2, 256, 1, 6, 8},
     {1, 256, 1, 4, 8},
+    {2, 128, 1, 8, 4},   // 256 x 128 pair tile: fewest operand bytes per SM among the small tiles
 };
 
 struct DeviceState {
@@ -203,9 +204,11 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // tiles run at the same rate within 1 %, and the 256 x 512 tile, whose accumulator fills TMEM,
 // loses about one K block per tile because its next tile cannot start before the accumulator is
 // drained.  So short K and bad wave counts go to the 256 x 256 tile, the rest to the wider one.
-constexpr int kAutoConfigs = 4;                       // candidates of the automatic choice
-constexpr double kConfigRate[kAutoConfigs] = {0.99, 1.0, 0.72, 0.5};
-constexpr double kTileBoundaryKBlocks[kAutoConfigs] = {0.0, 1.0, 0.0, 0.0};
+// Per configuration; rate 0 = not a candidate of the automatic choice (test / experiment variants).
+// The 256 x 128 pair tile (7) only matters when a problem has too few tiles for anything wider:
+// it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).
+constexpr double kConfigRate[kNumConfigs] = {0.99, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 1.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0};
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
 constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2; }
@@ -215,7 +218,7 @@ constexpr bool has_even_split(int config) { return config == 0 || config == 2; }
 // configuration's tile: about 12 us measured on B200 (counters zeroed by a memset node, partial
 // tiles written, the wait for the other contributors, one tile's worth of partial data read back
 // and stored; little of it overlaps the next unit's main loop).
-constexpr double kEvenSplitFixupKBlocks[kAutoConfigs] = {43.0, 0.0, 32.0, 0.0};
+constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 
 struct Plan {
   int config = 0;
@@ -236,12 +239,13 @@ inline int grid_cap(const ConfigInfo& c, int sm_count) {
 
 // The K-split schedule gives every CTA the same number of K blocks; it pays when whole tiles
 // quantise badly over the SMs (few tiles, as in the memory-bound small-M shapes) and K is long.
-Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true) {
+Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int config_limit = kNumConfigs) {
   Plan best;
   double best_cost = 1e300;
   const long k_blocks = ceil_div(K, 64);
   const int first = (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) ? static_cast<int>(g_opt_tile_config) : 0;
-  const int last = (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) ? first + 1 : kAutoConfigs;
+  const bool forced_config = g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs;
+  const int last = forced_config ? first + 1 : config_limit;   // config_limit: callers whose kernels exist for the first few configurations only
   for (int i = first; i < last; ++i) {
     const ConfigInfo& c = kConfigs[i];
     const int block_n = c.mma_n * c.halves;
@@ -249,12 +253,13 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true) {
     const int cap = grid_cap(c, sm_count);
     const long slots = cap / c.cta_group;
     const long waves = ceil_div(tiles, slots);
-    const double rate = i < kAutoConfigs ? kConfigRate[i] : 1.0;
+    if (!forced_config && kConfigRate[i] <= 0.0) continue;
+    const double rate = kConfigRate[i] > 0.0 ? kConfigRate[i] : 1.0;
     Plan cand;
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
     // costs in units of (one K block of one tile column) per CTA
-    const double boundary = i < kAutoConfigs ? kTileBoundaryKBlocks[i] : 0.0;
+    const double boundary = kTileBoundaryKBlocks[i];
     double cost = static_cast<double>(waves) * block_n * (k_blocks + boundary) / rate;
     const long units = tiles * k_blocks;
     // K-split.  Forced (split_k = 1): as many ranges as CTA (pair)s.  Automatic: the 128 x 256
@@ -581,6 +586,7 @@ int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cuda
     case 4: return launch_config<4, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 5: return launch_config<5, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 6: return launch_config<6, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 7: return launch_config<7, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }
@@ -761,8 +767,8 @@ int gemm_sm100_gemm_scaled(const void* A, const void* B, void* C, int M, int N, 
     rc = get_encoder(cuda_error_out);
     if (rc != GEMM_SM100_OK) return rc;
   }
-  Plan plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false);
-  if (plan.config > 3) plan = Plan{};       // the experimental configurations have no such variant
+  Plan plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false, /*config_limit=*/4);
+  if (plan.config > 3) plan = Plan{};       // (a forced configuration without such a variant)
   if (plan.ctas == 0) {
     const long tiles = ceil_div(M, 256L) * ceil_div(N, 256L);
     const long slots = st->sm_count / 2;
