@@ -863,44 +863,42 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               const int colc = n_tile * Cfg::kBlockN + bc * Cfg::kEpiCols;
               if (row >= p.M || colc >= p.N || (kDebug && (dbg & kDebugSkipStores))) continue;
               uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)row * p.ldc + colc;
+              // the whole 64-column chunk of one contributor at a time: sixteen loads in flight per lane
+              float4 acc[16];
 #pragma unroll 1
-              for (int half = 0; half < 2; ++half) {              // 32 columns at a time: eight loads in flight
-                float4 acc[8];
-#pragma unroll 1
-                for (int i = 0; i < sk_factor; ++i) {
-                  const float4* src = reinterpret_cast<const float4*>(
-                                          p.sk_partials + ((size_t)(seg.tile * sk_factor + i) * G + cta_rank) * partial_floats) +
-                                      (size_t)(bc * 16 + half * 8) * sk_rows + bq * 32 + lane;
-                  float4 t[8];
+              for (int i = 0; i < sk_factor; ++i) {
+                const float4* src = reinterpret_cast<const float4*>(
+                                        p.sk_partials + ((size_t)(seg.tile * sk_factor + i) * G + cta_rank) * partial_floats) +
+                                    (size_t)(bc * 16) * sk_rows + bq * 32 + lane;
+                float4 t[16];
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) t[j] = __ldcg(src + (size_t)j * sk_rows);
+                for (int j = 0; j < 16; ++j) t[j] = __ldcg(src + (size_t)j * sk_rows);
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    if (i == 0) {
-                      acc[j] = t[j];
-                    } else {
-                      acc[j].x += t[j].x;
-                      acc[j].y += t[j].y;
-                      acc[j].z += t[j].z;
-                      acc[j].w += t[j].w;
-                    }
+                for (int j = 0; j < 16; ++j) {
+                  if (i == 0) {
+                    acc[j] = t[j];
+                  } else {
+                    acc[j].x += t[j].x;
+                    acc[j].y += t[j].y;
+                    acc[j].z += t[j].z;
+                    acc[j].w += t[j].w;
                   }
                 }
+              }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {                     // 8 columns = 16 bytes of C per step
-                  const int col = colc + half * 32 + j * 8;
-                  const uint32_t w0 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].x), __float_as_uint(acc[2 * j].y));
-                  const uint32_t w1 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].z), __float_as_uint(acc[2 * j].w));
-                  const uint32_t w2 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j + 1].x), __float_as_uint(acc[2 * j + 1].y));
-                  const uint32_t w3 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j + 1].z), __float_as_uint(acc[2 * j + 1].w));
-                  if (col + 8 <= p.N) {
-                    *reinterpret_cast<uint4*>(crow + half * 32 + j * 8) = make_uint4(w0, w1, w2, w3);
-                  } else {
-                    const uint32_t w[4] = {w0, w1, w2, w3};
+              for (int j = 0; j < 8; ++j) {                       // 8 columns = 16 bytes of C per step
+                const int col = colc + j * 8;
+                const uint32_t w0 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].x), __float_as_uint(acc[2 * j].y));
+                const uint32_t w1 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].z), __float_as_uint(acc[2 * j].w));
+                const uint32_t w2 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j + 1].x), __float_as_uint(acc[2 * j + 1].y));
+                const uint32_t w3 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j + 1].z), __float_as_uint(acc[2 * j + 1].w));
+                if (col + 8 <= p.N) {
+                  *reinterpret_cast<uint4*>(crow + j * 8) = make_uint4(w0, w1, w2, w3);
+                } else {
+                  const uint32_t w[4] = {w0, w1, w2, w3};
 #pragma unroll
-                    for (int t2 = 0; t2 < 8; ++t2)
-                      if (col + t2 < p.N) crow[half * 32 + j * 8 + t2] = (uint16_t)(w[t2 >> 1] >> (16 * (t2 & 1)));
-                  }
+                  for (int t2 = 0; t2 < 8; ++t2)
+                    if (col + t2 < p.N) crow[j * 8 + t2] = (uint16_t)(w[t2 >> 1] >> (16 * (t2 & 1)));
                 }
               }
             }
