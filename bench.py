@@ -40,9 +40,10 @@ sys.path.insert(0, str(REPO / "cute-examples_b200"))
 
 import torch  # noqa: E402
 
-# DRAM traffic of one launch of the N=1 workload (M=N=K=8192): dram__bytes_read.sum +
-# dram__bytes_write.sum from an ncu capture of this kernel on this workload, mean of two launches.
-NCU_DRAM_BYTES_PER_LAUNCH_8192 = 985_000_000
+# DRAM traffic of one launch of the N=1 workload comes from an ncu capture recorded in
+# profiles/dram_traffic.json together with the kernel configuration it was taken with; a record
+# whose configuration no longer matches what the library selects is reported as stale (null).
+TRAFFIC_RECORD = REPO / "profiles" / "dram_traffic.json"
 
 WORKLOAD_SINGLE = "cfg2 square bf16 TN GEMM M=N=K=8192, fp32 accumulate, bf16 out, seed 1"
 
@@ -64,6 +65,27 @@ def load_peaks():
         except Exception:
             pass
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def recorded_traffic(key, live_config):
+    """(bytes per launch or None, note) from profiles/dram_traffic.json for workload `key`."""
+    try:
+        rec = json.loads(TRAFFIC_RECORD.read_text())[key]
+    except Exception as exc:  # missing file or workload
+        return None, f"no ncu record for {key} ({exc.__class__.__name__})"
+    if rec.get("tile_config") != live_config:
+        return None, (f"stale: {TRAFFIC_RECORD.name} was captured with [{rec.get('tile_config')}], the library now "
+                      f"selects [{live_config}]")
+    return int(rec["dram_bytes_per_launch"]), rec.get("source", "")
+
+
+def base_config(gpus):
+    """The `config` object both arms print (same keys and values for the same --gpus)."""
+    if gpus == 1:
+        return {"workload": WORKLOAD_SINGLE, "M": 8192, "N": 8192, "K": 8192,
+                "l2": "operands 256 MiB > 126 MB L2 (inputs larger than L2; no flush between steps)"}
+    return {"workload": workload_multi(gpus), "M": 32768, "N": 32768, "K": 32768,
+            "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"}
 
 
 def gemm_flops(M, N, K):
@@ -153,6 +175,63 @@ def device_inputs(M, N, K, seed, dtype, device, a_std=None, b_std=None):
     A = (torch.randn((M, K), generator=g, device=device, dtype=torch.float32) * sa).to(dtype)
     B = (torch.randn((N, K), generator=g, device=device, dtype=torch.float32) * sb).to(dtype)
     return A, B
+
+
+def cfg5_operands(device, n=32768, b_rows=None, slab=4096):
+    """Benchmark configuration 5 operands, seed 4: A[n,n] then B[n,n] ~ N(0,1)/sqrt(n) from ONE device
+    generator, drawn as fp32 slabs of `slab` rows (0.5 GiB of scratch at a time) and cast to bf16.
+    Every caller draws the identical sequence; `b_rows = (lo, hi)` keeps only those rows of B, so
+    the ranks of a column-sharded run hold row slabs of the same B that one GPU would use."""
+    g = torch.Generator(device=device).manual_seed(4)
+    lo, hi = (0, n) if b_rows is None else b_rows
+    A = torch.empty((n, n), dtype=torch.bfloat16, device=device)
+    B = torch.empty((hi - lo, n), dtype=torch.bfloat16, device=device)
+    scale = 1.0 / n ** 0.5
+    for r0 in range(0, n, slab):
+        A[r0:r0 + slab] = (torch.randn((slab, n), generator=g, device=device) * scale).to(torch.bfloat16)
+    for r0 in range(0, n, slab):
+        draw = torch.randn((slab, n), generator=g, device=device)       # drawn even when not kept: same stream
+        a, b = max(r0, lo), min(r0 + slab, hi)
+        if a < b:
+            B[a - lo:b - lo] = (draw[a - r0:b - r0] * scale).to(torch.bfloat16)
+        del draw
+    return A, B
+
+
+def sampled_rows_error(C_rows, A_rows, B):
+    """Normalised max error of sampled rows of C against the CPU oracle (the reference's check
+    expression) on the same operands; returns (error, rows checked)."""
+    from oracle import oracle
+
+    C_ref = oracle.reference_matmul_fp32(A_rows.cpu(), B.cpu())
+    return oracle.normalized_max_error(C_rows.cpu(), C_ref), int(A_rows.shape[0])
+
+
+def cfg5_single_gpu(gk, peaks, device, steps=5, warmup=3, with_cpu=True):
+    """Benchmark configuration 5 (M=N=K=32768) on ONE GPU: the strong-scaling baseline of the
+    multi-GPU runs, same operands (seed 4), timed back to back (a launch takes about 50 ms, so
+    this is the sustained, power-capped regime and the sustained cuBLAS peak is the divisor)."""
+    n = 32768
+    A, B = cfg5_operands(device, n)
+    C = torch.empty((n, n), dtype=torch.bfloat16, device=device)
+    for _ in range(warmup):
+        gk.gemm_tn_test(A, B, C)
+    torch.cuda.synchronize()
+    ms = time_steps(lambda: gk.gemm_tn_test(A, B, C), steps, torch.cuda.synchronize) / steps
+    gk.device_status()
+    tf = gemm_flops(n, n, n) / ms / 1e9
+    peak = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"])
+    rec = {"shape": "cfg5 32768^3 bf16 (1 GPU)", "ms": round(ms, 3), "tflops": round(tf, 1),
+           "gbs": round(gemm_bytes(n, n, n) / ms / 1e6, 1), "bound": "tensor", "steps": steps, "warmup": warmup,
+           "l2": "operands 4 GiB > L2, back to back", "frac": round(tf / peak, 4), "peak": "bf16_tflops_sustained",
+           "note": "the same workload the --gpus N runs split over N GPUs: efficiency = value_N / (N x this)"}
+    if with_cpu:
+        rows = torch.tensor([0, 255, 256, 9999, 16384, 20000, 32767, 12345, 4097, 8191, 30000, 77, 25000, 1, 511, 31999])
+        err, count = sampled_rows_error(C[rows.to(device)], A[rows.to(device)], B)
+        rec["norm_max_err"] = float(f"{err:.3e}")
+        rec["rows_checked"] = count
+    del A, B, C
+    return rec
 
 
 def time_steps(fn, steps, sync, barrier=None):
@@ -271,12 +350,17 @@ def run_reference(args, rank):
         return
     from oracle import oracle
 
-    if args.gpus == 1:
-        M = N = K = 8192
-        seed, workload = 1, WORKLOAD_SINGLE
-    else:
-        M = N = K = 32768
-        seed, workload = 4, workload_multi(args.gpus)
+    # All host cores, whatever the launcher exported (torchrun sets OMP_NUM_THREADS=1 for its
+    # children, which made this arm 16x slower at N > 1 than at N = 1).
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(cores)
+    cfg = base_config(args.gpus)
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    seed = 1 if args.gpus == 1 else 4
     rows = 1024 if args.gpus == 1 else 256
     A, B = oracle.make_inputs(rows, N, K, seed, torch.bfloat16)
     for _ in range(min(args.warmup, 2)):
@@ -286,14 +370,14 @@ def run_reference(args, rank):
         oracle.reference_matmul_fp32(A, B)
     sec = (time.perf_counter() - t0) / args.steps
     tf = gemm_flops(rows, N, K) / sec / 1e12
-    sample = (f"each step = torch fp32 matmul of a {rows}-row slab of A x all of B (N={N}, K={K}); "
-              f"TFLOP/s of the slab stands for the whole GEMM")
+    sample = (f"each step = torch fp32 matmul of a {rows}-row slab of A x all of B (N={N}, K={K}) on "
+              f"{torch.get_num_threads()} threads; TFLOP/s of the slab stands for the whole GEMM")
     line = {
         "impl": "reference", "metric": "bf16 GEMM TFLOP/s", "value": round(tf, 4), "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, "M": M, "N": N, "K": K, "sample_rows": rows},
+        "config": cfg,
         "cpu_baseline": {"value": round(tf, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": sample},
         "e2e": {"value": round(tf, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -346,8 +430,17 @@ def run_single(args):
     e2e_check = float((Ch[::1024].float() - C[::1024].cpu().float()).abs().max().item())
     del host_gemm
 
+    del A, B, C, Ah, Bh, Ch
+    torch.cuda.empty_cache()
     shapes = [] if args.no_shapes else secondary_shapes(gk, peaks, device, with_cpu=not args.no_cpu)
+    scaling_baseline = None
+    if not args.no_shapes:
+        torch.cuda.empty_cache()
+        scaling_baseline = cfg5_single_gpu(gk, peaks, device, with_cpu=not args.no_cpu)
+        shapes.append(scaling_baseline)
     cpu = None if args.no_cpu else cpu_baseline_sample(M, N, K, 1, rows=2048)
+    live_config = gk.describe_config(gk.select_config(M, N, K, 0))
+    traffic, traffic_note = recorded_traffic("8192x8192x8192_bf16", live_config)
 
     timed_s = ms_total / 1e3
     peak_key = "bf16_tflops" if timed_s <= 1.0 else "bf16_tflops_sustained"
@@ -357,9 +450,8 @@ def run_single(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD_SINGLE,
-                   "M": M, "N": N, "K": K, "tile_config": gk.describe_config(gk.select_config(M, N, K, 0)),
-                   "l2": "operands 256 MiB > 126 MB L2 (inputs larger than L2; no flush between steps)"},
+        "config": base_config(1),
+        "kernel_config": live_config,
         "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
                 "api": "gemm_kernels.HostGemm (A uploaded in row panels; GEMM and download of C per panel)",
@@ -371,16 +463,30 @@ def run_single(args):
                             "fast power-cap steps); kernel_cycles: SM cycles of one launch from the kernel's "
                             "trace counters; sm_mhz_effective = kernel_cycles / ms_per_step"),
         "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": peak, "unit": "TFLOP/s",
-                     "frac": round(tflops / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH_8192,
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this "
-                                       "workload (profiles/gemm_tn_kernel_256x512_bf16_8192cubed_ncu_full.md); "
-                                       "algorithmic bytes 4.03e8",
+                     "frac": round(tflops / peak, 4), "traffic": traffic,
+                     "traffic_source": traffic_note, "algorithmic_bytes": gemm_bytes(M, N, K),
                      "peak_source": f"{peak_src}:{peak_key}", "kernel": "gemm_sm100::gemm_tn_kernel",
                      "flops_per_launch": gemm_flops(M, N, K)},
         "cpu_baseline": cpu,
+        "scaling_baseline": scaling_baseline,
         "shapes": shapes,
     }
     print(json.dumps(line), flush=True)
+
+
+def c_checksums(C, chunk_rows=2048):
+    """Two position-sensitive 64-bit checksums of the bits of C (computed in row chunks so that the
+    int64 temporaries stay small): equal on two GPUs only if they hold the same C, bit for bit."""
+    M, N = C.shape
+    col_w = (torch.arange(N, device=C.device, dtype=torch.int64) % 251) + 1
+    plain = torch.zeros((), dtype=torch.int64, device=C.device)
+    weighted = torch.zeros((), dtype=torch.int64, device=C.device)
+    for r0 in range(0, M, chunk_rows):
+        bits = C[r0:r0 + chunk_rows].view(torch.int16).to(torch.int64)
+        plain += bits.sum()
+        row_w = (torch.arange(r0, r0 + bits.shape[0], device=C.device, dtype=torch.int64) % 241) + 1
+        weighted += ((bits * col_w).sum(dim=1) * row_w).sum()
+    return torch.stack([plain, weighted])
 
 
 def run_multi(args):
@@ -395,13 +501,12 @@ def run_multi(args):
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", device_id=device)
     peaks, peak_src = load_peaks()
-    M = N = K = 32768
+    cfg = base_config(world)
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
     dtype = torch.bfloat16
     lo, hi = gk.shard_rows(N, world, rank)
-    g = torch.Generator(device=device).manual_seed(4)          # same A on every rank
-    A = (torch.randn((M, K), generator=g, device=device, dtype=torch.float32) / K ** 0.5).to(dtype)
-    gb = torch.Generator(device=device).manual_seed(4000 + rank)
-    B_shard = (torch.randn((hi - lo, K), generator=gb, device=device, dtype=torch.float32) / K ** 0.5).to(dtype)
+    # A (same on every rank) and this rank's rows [lo, hi) of the seed-4 B
+    A, B_shard = cfg5_operands(device, N, b_rows=(lo, hi))
     # Default: the all-gather of C folded into the GEMM epilogue (stores to every GPU's C over
     # NVLink, symmetric memory).  --nsplit nccl: per-panel GEMM + NCCL all-gather + re-stride copy.
     mode = args.nsplit
@@ -416,15 +521,15 @@ def run_multi(args):
             print(f"[bench] symmetric memory unavailable ({exc!r}); using the NCCL all-gather path", file=sys.stderr)
             mode = "nccl"
     if mode == "fused":
-        C = fused.C
         launches_per_step = 1
         step = lambda: fused(A, B_shard)  # noqa: E731
-        how = "all-gather of C fused into the GEMM epilogue (TMA stores to every GPU's C over NVLink)"
+        how = ("all-gather of C fused into the GEMM epilogue (TMA stores to every GPU's C over NVLink), "
+               "two alternating C buffers, one cross-GPU barrier per step")
     else:
-        C = torch.empty((M, N), dtype=dtype, device=device)
+        C_nccl = torch.empty((M, N), dtype=dtype, device=device)
         plan = gk.NSplitPlan.create(M, N, world, dtype, device, num_panels=args.panels)
         launches_per_step = plan.num_panels
-        step = lambda: gk.gemm_tn_nsplit(A, B_shard, C, plan=plan)  # noqa: E731
+        step = lambda: gk.gemm_tn_nsplit(A, B_shard, C_nccl, plan=plan)  # noqa: E731
         how = f"NCCL all-gather of C, {plan.num_panels} row panels overlapped with the GEMM"
 
     def barrier():
@@ -441,22 +546,63 @@ def run_multi(args):
     ms = t.item() / args.steps
     tflops = gemm_flops(M, N, K) / ms / 1e9
 
-    def per_rank(total_ms):
-        mine = torch.tensor([total_ms / args.steps], dtype=torch.float64, device=device)
-        every = torch.zeros(world, dtype=torch.float64, device=device)
-        dist.all_gather_into_tensor(every, mine)
-        return [round(x, 4) for x in every.tolist()]
+    # ---- parity of what was just timed: the assembled C of the last step
+    C = step()
+    torch.cuda.synchronize()
+    barrier()
+    # (1) this rank's own column slab of its C against the CPU oracle on sampled rows of A
+    rows = torch.tensor([0, 255, 256, 9999, 16384, 20000, 32767, 12345, 4097, 8191, 30000, 77, 25000, 1, 511, 31999])
+    rows_d = rows.to(device)
+    err, rows_checked = sampled_rows_error(C[rows_d][:, lo:hi], A[rows_d], B_shard)
+    errs = torch.zeros(world, dtype=torch.float64, device=device)
+    dist.all_gather_into_tensor(errs, torch.tensor([err], dtype=torch.float64, device=device))
+    nan_count = torch.isnan(C[rows_d].float()).sum()
+    dist.all_reduce(nan_count)
+    # (2) every rank holds the same full C: position-sensitive checksums of all of C must agree
+    sums = c_checksums(C)
+    every = torch.zeros((world, 2), dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(every, sums.view(1, 2))
+    ranks_equal = bool((every == every[0]).all().item())
+    parity = {"norm_max_err": float(f"{errs.max().item():.3e}"), "tolerance": 2e-2,
+              "rows_checked_per_rank": rows_checked, "columns_checked": "each rank its own slab: all N columns",
+              "nan_in_sampled_rows": int(nan_count.item()), "ranks_equal": ranks_equal,
+              "checksums_rank0": [int(v) for v in every[0].tolist()],
+              "ok": bool(errs.max().item() <= 2e-2 and ranks_equal and int(nan_count.item()) == 0)}
 
-    # this rank's GEMM alone (no exchange), same number of steps: shows what the exchange costs
+    def per_rank(total_ms, steps):
+        mine = torch.tensor([total_ms / steps], dtype=torch.float64, device=device)
+        every_ms = torch.zeros(world, dtype=torch.float64, device=device)
+        dist.all_gather_into_tensor(every_ms, mine)
+        return [round(x, 4) for x in every_ms.tolist()]
+
+    # ---- this rank's slab GEMM alone (no exchange) in alternation with cuBLAS on the same slab:
+    # what the exchange costs, and whether a low per-GPU figure is this kernel or the box's state
     C_slab = torch.empty((M, hi - lo), dtype=dtype, device=device)
+    C_mm = torch.empty((M, hi - lo), dtype=dtype, device=device)
     local_step = lambda: gk.gemm_tn_test(A, B_shard, C_slab)  # noqa: E731
+    mm_step = lambda: torch.mm(A, B_shard.T, out=C_mm)  # noqa: E731
     local_step()
-    local_total = time_steps(local_step, args.steps, torch.cuda.synchronize, barrier)
-    t = torch.tensor([local_total], dtype=torch.float64, device=device)
+    mm_step()
+    barrier()
+    torch.cuda.synchronize()
+    ours_ms, mm_ms = [], []
+    for _ in range(args.steps):
+        for fn, acc in ((local_step, ours_ms), (mm_step, mm_ms)):
+            s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_ev.record()
+            fn()
+            e_ev.record()
+            e_ev.synchronize()
+            acc.append(s_ev.elapsed_time(e_ev))
+    gk.device_status()
+    local_total, mm_total = sum(ours_ms), sum(mm_ms)
+    t = torch.tensor([local_total, mm_total], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    local_ms = t.item() / args.steps
-    local_ms_per_rank = per_rank(local_total)
-    del C_slab
+    local_ms, cublas_ms = t[0].item() / args.steps, t[1].item() / args.steps
+    local_ms_per_rank = per_rank(local_total, args.steps)
+    cublas_ms_per_rank = per_rank(mm_total, args.steps)
+    slab_max_diff = float((C_slab[rows_d].float() - C_mm[rows_d].float()).abs().max().item())
+    del C_slab, C_mm
 
     # end to end: operands start in pinned host memory, the result ends there, every step.  The
     # host holds ONE copy of A, B and C between the ranks: rank g uploads its 1/G of A's rows and
@@ -470,8 +616,8 @@ def run_multi(args):
         A[a_lo:a_hi].copy_(Ah, non_blocking=True)
         B_shard.copy_(Bh, non_blocking=True)
         dist.all_gather_into_tensor(A, A[a_lo:a_hi])
-        step()
-        Ch.copy_(C[:, lo:hi], non_blocking=True)
+        out = step()
+        Ch.copy_(out[:, lo:hi], non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 3))
     e2e_step()
@@ -490,15 +636,21 @@ def run_multi(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": workload_multi(world), "exchange": how,
-                       "M": M, "N": N, "K": K, "nsplit_mode": mode,
-                       "per_gpu_tflops": round(per_gpu, 2),
-                       "local_gemm_ms_per_step": round(local_ms, 4),
-                       "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange",
-                       "local_gemm_ms_per_rank": local_ms_per_rank,
-                       "local_gemm_per_rank_note": "the GPUs of a box differ under the power cap; a step that "
-                                                   "ends in a cross-GPU barrier runs at the slowest one's pace",
-                       "l2": "operands 2 GiB + 2/G GiB per GPU > 126 MB L2 (inputs larger than L2)"},
+            "config": cfg,
+            "parity": parity,
+            "details": {"exchange": how, "nsplit_mode": mode, "per_gpu_tflops": round(per_gpu, 2),
+                        "local_gemm_ms_per_step": round(local_ms, 4),
+                        "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange, timed "
+                                           "launch by launch in alternation with cuBLAS (torch.mm) on the same slab",
+                        "local_gemm_ms_per_rank": local_ms_per_rank,
+                        "cublas_slab_ms_per_step": round(cublas_ms, 4),
+                        "cublas_slab_ms_per_rank": cublas_ms_per_rank,
+                        "ours_over_cublas_time": round(local_ms / cublas_ms, 4),
+                        "slab_max_abs_diff_vs_cublas": slab_max_diff,
+                        "exchange_overhead": round(ms / local_ms - 1.0, 4),
+                        "exchange_overhead_note": "fused step time / slowest rank's plain slab GEMM - 1; the GPUs of a "
+                                                  "box differ under the power cap and a step that ends in a cross-GPU "
+                                                  "barrier runs at the slowest one's pace"},
             "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,
                     "note": "bytes summed over ranks: rank g uploads 1/G of A (replicated over NVLink by an "
@@ -508,8 +660,9 @@ def run_multi(args):
             "clocks": clk.summary(),
             "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": peak, "unit": "TFLOP/s",
                          "frac": round(per_gpu / peak, 4), "traffic": None,
-                         "peak_source": f"{peak_src}:bf16_tflops_sustained", "kernel": "gemm_sm100::gemm_tn_kernel",
-                         "note": "per-GPU TFLOP/s of the whole step (GEMM + exchange of C + barriers)"},
+                         "peak_source": f"{peak_src}:bf16_tflops_sustained", "kernel": "gemm_sm100::gemm_tn_fanout_kernel"
+                         if mode == "fused" else "gemm_sm100::gemm_tn_kernel",
+                         "note": "per-GPU TFLOP/s of the whole step (GEMM + exchange of C + barrier)"},
             "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)

@@ -41,9 +41,9 @@ def _nvcc() -> str:
 
 def _cxx() -> str:
     """Host compiler of the torch binding.  GEMM_KERNELS_CXX overrides; otherwise the system g++ is
-    preferred over $CXX: a $CXX wrapper that re-orders the C++ standard include directories
-    (seen as /opt/gcc/bin/g++ in some images) produced a binding whose error messages with
-    integer arguments crashed inside iostream formatting."""
+    preferred over $CXX: a $CXX compiler wrapper that re-orders the C++ standard include
+    directories produced a binding whose error messages with integer arguments crashed inside
+    iostream formatting."""
     override = os.environ.get("GEMM_KERNELS_CXX")
     if override:
         return override
@@ -96,8 +96,13 @@ def build_torch_binding(force: bool = False, verbose: bool = False) -> Path:
 
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     includes = ce.include_paths() + [sysconfig.get_paths()["include"], f"{cuda_home}/include"]
+    import torch
+
+    # The macros torch's own extension builder passes: above all the libstdc++ ABI the installed
+    # torch was built with (std::string crosses the boundary in error messages and option names).
     cmd = [_cxx(), "-O3", "-Wall", "-Wextra", "-std=c++17", "-fPIC", "-shared",
-           "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+           "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
     for inc in includes:
         cmd += ["-isystem", inc]
     cmd += [str(src), "-o", str(out)]

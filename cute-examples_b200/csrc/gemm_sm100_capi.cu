@@ -17,6 +17,7 @@
 #include <cstring>
 #include <atomic>
 #include <mutex>
+#include <utility>
 
 #include "../../include/gemm_sm100.h"
 #include "gemm_tn_sm100.cuh"
@@ -35,7 +36,7 @@ constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 8;
+constexpr int kNumConfigs = 9;
 
 struct ConfigInfo {
   int cta_group, mma_n, halves, stages, epi_warps;
@@ -49,18 +50,18 @@ constexpr ConfigInfo kConfigs[kNumConfigs] = {
     {2, 256, 1, 6, 8},
     {1, 256, 1, 4, 8},
     {2, 128, 1, 8, 4},   // 256 x 128 pair tile: fewest operand bytes per SM among the small tiles
+    {2, 192, 1, 6, 4},   // 256 x 192 pair tile: for tile counts that quantise badly with 256 columns
 };
 
 struct DeviceState {
   bool ready = false;
+  int device = 0;
   int sm_count = 0;
   int cc_major = 0;
   unsigned int* status_ptr = nullptr;
   void* static_scratch = nullptr;      // device address of g_static_scratch on this device
   int max_ctas[kNumConfigs][2] = {};   // persistent grid limit per config and dtype
   bool attr_set[kNumConfigs][2] = {};
-  bool fanout_attr_set[2][2] = {};
-  bool nn_attr_set[4][2] = {};
 };
 
 std::mutex g_mutex;
@@ -74,8 +75,24 @@ std::atomic<long> g_opt_debug_flags{0};
 std::atomic<long> g_opt_group_m{0};
 std::atomic<long> g_opt_k_rotate{0};    // 0 never (default: measured no gain on B200), 1 always, -1 when there is a single tile row
 std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
-std::atomic<unsigned long long*> g_trace_ptr{nullptr};   // device buffer for per-CTA trace records, or null
-std::atomic<size_t> g_trace_bytes{0};
+// Bumped by every gemm_sm100_set_option: cached plans of an older generation are stale.
+std::atomic<unsigned> g_opt_generation{1};
+// Trace buffer (gemm_sm100_set_trace_buffer): pointer, size and the device that owns the memory,
+// kept together under g_mutex so that a launch reads a consistent triple.  Launches on any other
+// device ignore the buffer (its address means nothing there).
+struct TraceBuffer {
+  unsigned long long* ptr = nullptr;
+  size_t bytes = 0;
+  int device = -1;
+};
+TraceBuffer g_trace;
+std::atomic<bool> g_trace_on{false};   // fast check outside the mutex
+
+TraceBuffer trace_for_device(int device) {
+  if (!g_trace_on.load(std::memory_order_acquire)) return TraceBuffer{};
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return g_trace.device == device ? g_trace : TraceBuffer{};
+}
 
 // Optional overrides from the environment, read once when the library is loaded:
 // GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M, GEMM_SM100_MAX_CTAS,
@@ -143,6 +160,46 @@ int encode_2d(CUtensorMap* map, const void* base, int dtype, long rows, long col
   return GEMM_SM100_OK;
 }
 
+// Per-thread cache of encoded tensor maps.  The encoding depends only on the arguments below, so
+// a caller that multiplies the same buffers again (a layer of a model, a benchmark loop) skips the
+// driver's encoder: three calls of roughly a microsecond each per launch, which is most of the host
+// cost of a small GEMM (the reference rebuilds all three maps on every call, gemm_test.cu:56-68).
+struct MapKey {
+  const void* base;
+  long rows, cols, ld;
+  int box_rows, dtype;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           dtype == o.dtype;
+  }
+};
+struct MapCache {
+  static constexpr int kEntries = 32;
+  MapKey keys[kEntries] = {};
+  CUtensorMap maps[kEntries];
+  bool used[kEntries] = {};
+  unsigned next = 0;
+};
+thread_local MapCache t_map_cache;
+
+int encode_2d_cached(CUtensorMap* map, const void* base, int dtype, long rows, long cols, long ld, int box_rows,
+                     int* cuda_error_out) {
+  MapCache& c = t_map_cache;
+  const MapKey key{base, rows, cols, ld, box_rows, dtype};
+  for (int i = 0; i < MapCache::kEntries; ++i)
+    if (c.used[i] && c.keys[i] == key) {
+      std::memcpy(map, &c.maps[i], sizeof(CUtensorMap));
+      return GEMM_SM100_OK;
+    }
+  const int rc = encode_2d(map, base, dtype, rows, cols, ld, box_rows, cuda_error_out);
+  if (rc != GEMM_SM100_OK) return rc;
+  const unsigned slot = c.next++ % MapCache::kEntries;
+  c.keys[slot] = key;
+  std::memcpy(&c.maps[slot], map, sizeof(CUtensorMap));
+  c.used[slot] = true;
+  return GEMM_SM100_OK;
+}
+
 int device_state(DeviceState** out, int* cuda_error_out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -159,8 +216,10 @@ int device_state(DeviceState** out, int* cuda_error_out) {
     e = cudaGetSymbolAddress(&p, g_status_word);
     if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
     st.status_ptr = static_cast<unsigned int*>(p);
-    e = cudaMemset(st.status_ptr, 0, sizeof(unsigned int));
-    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    st.device = dev;
+    // No memset: a __device__ variable without an initialiser starts at zero when its module is
+    // loaded, so the first call on a device issues no synchronous work (it may come while another
+    // stream is being captured).
     st.ready = true;
   }
   *out = &st;
@@ -207,18 +266,25 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // Per configuration; rate 0 = not a candidate of the automatic choice (test / experiment variants).
 // The 256 x 128 pair tile (7) only matters when a problem has too few tiles for anything wider:
 // it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).
-constexpr double kConfigRate[kNumConfigs] = {0.99, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545};
-constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 1.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0};
+constexpr double kConfigRate[kNumConfigs] = {0.99, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545, 0.955};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 1.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0};
+// Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
+// in K blocks of that tile.
+constexpr double kFanoutKBlocksPerOutput = 12.0;
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
 constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2; }
 // Configurations whose K-split kernel also has the even split (single-width tiles).
 constexpr bool has_even_split(int config) { return config == 0 || config == 2; }
+// Configurations with a store-to-every-output kernel (the pair tiles of the multi-GPU path).
+constexpr bool has_fanout(int config) { return config == 0 || config == 1; }
+// Configurations with kernels for the other operand layouts and alpha / beta.
+constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // Even split: what cutting costs per wave of units on top of the K blocks, in K blocks of the
 // configuration's tile: about 12 us measured on B200 (counters zeroed by a memset node, partial
 // tiles written, the wait for the other contributors, one tile's worth of partial data read back
 // and stored; little of it overlaps the next unit's main loop).
-constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 
 struct Plan {
   int config = 0;
@@ -336,6 +402,32 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
   return best;
 }
 
+// Per-thread cache of plans: the binding asks for the workspace size and then launches, and callers
+// repeat shapes, so the cost model runs once per (shape, option state).
+Plan plan_for(int M, int N, int K, int sm_count, bool allow_split = true, int config_limit = kNumConfigs) {
+  struct Entry {
+    int M = -1, N = 0, K = 0, sm = 0, limit = 0;
+    bool allow = false;
+    unsigned generation = 0;
+    Plan plan;
+  };
+  constexpr int kEntries = 16;
+  thread_local Entry cache[kEntries];
+  thread_local unsigned next = 0;
+  const unsigned generation = g_opt_generation.load(std::memory_order_acquire);
+  for (int i = 0; i < kEntries; ++i) {
+    const Entry& e = cache[i];
+    if (e.M == M && e.N == N && e.K == K && e.sm == sm_count && e.limit == config_limit && e.allow == allow_split &&
+        e.generation == generation)
+      return e.plan;
+  }
+  Entry& e = cache[next++ % kEntries];
+  e.M = M, e.N = N, e.K = K, e.sm = sm_count, e.limit = config_limit, e.allow = allow_split;
+  e.generation = generation;
+  e.plan = make_plan(M, N, K, sm_count, allow_split, config_limit);
+  return e.plan;
+}
+
 // Tile counts, rasterisation and wait limit of one launch (everything that does not depend on
 // the schedule variant).
 template <class Cfg>
@@ -366,89 +458,9 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   return tp;
 }
 
-template <int kCfgIndex, bool kIsBf16>
-int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceState& st, cudaStream_t stream,
-                  int* cuda_error_out) {
-  constexpr ConfigInfo ci = kConfigs[kCfgIndex];
-  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
-  // The instrumented instantiation runs only while a trace buffer or an experiment flag is set.
-  const bool debug = g_trace_ptr.load() != nullptr || g_opt_debug_flags.load() != 0;
-  auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
-  if constexpr (has_split_k(kCfgIndex)) {
-    if (plan.split_k) kernel = gemm_tn_kernel<Cfg, false, true>;
-  }
-  constexpr int dt = kIsBf16 ? 0 : 1;
-  cudaError_t e;
-
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (!st.attr_set[kCfgIndex][dt]) {
-      e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-      e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-      if constexpr (has_split_k(kCfgIndex)) {
-        e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::kSmemBytes);
-        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-      }
-      int max_ctas = st.sm_count;
-      if (Cfg::kCtaGroup == 2) {
-        cudaLaunchConfig_t qc = {};
-        qc.gridDim = dim3(st.sm_count - st.sm_count % 2);
-        qc.blockDim = dim3(Cfg::kThreads);
-        qc.dynamicSmemBytes = Cfg::kSmemBytes;
-        cudaLaunchAttribute qa[1];
-        qa[0].id = cudaLaunchAttributeClusterDimension;
-        qa[0].val.clusterDim.x = 2;
-        qa[0].val.clusterDim.y = 1;
-        qa[0].val.clusterDim.z = 1;
-        qc.attrs = qa;
-        qc.numAttrs = 1;
-        int clusters = 0;
-        e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &qc);
-        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-        if (clusters < 1) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
-        max_ctas = 2 * clusters;
-        if (max_ctas > st.sm_count) max_ctas = st.sm_count - st.sm_count % 2;
-      }
-      st.max_ctas[kCfgIndex][dt] = max_ctas;
-      st.attr_set[kCfgIndex][dt] = true;
-    }
-  }
-
-  TileParams tp = base_tile_params<Cfg>(p, st);
-  tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
-  tp.k_rotate = (g_opt_k_rotate > 0 || (g_opt_k_rotate < 0 && tp.m_tiles == 1 && !plan.split_k)) ? 1 : 0;
-  if (plan.split_k) {
-    tp.sk_flags = static_cast<unsigned int*>(workspace);
-    tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
-    tp.sk_rows = plan.partial_rows;
-    tp.sk_factor = plan.split_factor;
-    e = cudaMemsetAsync(tp.sk_flags, 0, plan.flag_bytes, stream);
-    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-  }
-
-  CUtensorMap map_a, map_b, map_c;
-  int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
-  if (rc) return rc;
-  rc = encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
-  if (rc) return rc;
-  rc = encode_2d(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
-  if (rc) return rc;
-
-  long ctas = plan.ctas;
-  if (ctas > st.max_ctas[kCfgIndex][dt]) {
-    // Fewer co-resident CTAs than SMs (never seen on B200).  The K-split schedule needs the
-    // grid it was planned for, because the workspace is indexed by CTA.
-    if (plan.split_k) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
-    ctas = st.max_ctas[kCfgIndex][dt];
-  }
-
-  unsigned long long* const trace_ptr = g_trace_ptr.load();
-  if (trace_ptr && g_trace_bytes.load() >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
-    tp.trace = trace_ptr;
-
+// Cluster launch of `kernel` on `ctas` CTAs of Cfg::kThreads threads.
+template <class Cfg, class Kernel, class... Args>
+cudaError_t launch_kernel(Kernel kernel, long ctas, cudaStream_t stream, const Args&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -461,7 +473,118 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   attrs[0].val.clusterDim.z = 1;
   cfg.attrs = attrs;
   cfg.numAttrs = Cfg::kCtaGroup == 2 ? 1 : 0;          // single-CTA tiles are launched without a cluster
-  e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// One-time set-up of a tile configuration on a device: the dynamic shared-memory limit of every
+// instantiation that can be launched for it, and how many CTAs of it are co-resident.
+template <int kCfgIndex, bool kIsBf16>
+int ensure_config(DeviceState& st, int* cuda_error_out) {
+  constexpr ConfigInfo ci = kConfigs[kCfgIndex];
+  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  constexpr int dt = kIsBf16 ? 0 : 1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (st.attr_set[kCfgIndex][dt]) return GEMM_SM100_OK;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::kSmemBytes);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  if constexpr (has_split_k(kCfgIndex)) {
+    e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  }
+  if constexpr (has_fanout(kCfgIndex)) {
+    e = cudaFuncSetAttribute(gemm_tn_fanout_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    e = cudaFuncSetAttribute(gemm_tn_fanout_kernel<Cfg, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  }
+  if constexpr (has_layouts(kCfgIndex)) {
+    for (auto k : {gemm_layout_kernel<Cfg, true, true>, gemm_layout_kernel<Cfg, true, false>,
+                   gemm_layout_kernel<Cfg, false, true>, gemm_layout_kernel<Cfg, false, false>}) {
+      e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    }
+  }
+  int max_ctas = st.sm_count;
+  if (Cfg::kCtaGroup == 2) {
+    cudaLaunchConfig_t qc = {};
+    qc.gridDim = dim3(st.sm_count - st.sm_count % 2);
+    qc.blockDim = dim3(Cfg::kThreads);
+    qc.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    qc.attrs = qa;
+    qc.numAttrs = 1;
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tn_kernel<Cfg, false>, &qc);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    if (clusters < 1) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
+    max_ctas = 2 * clusters;
+    if (max_ctas > st.sm_count) max_ctas = st.sm_count - st.sm_count % 2;
+  }
+  st.max_ctas[kCfgIndex][dt] = max_ctas;
+  st.attr_set[kCfgIndex][dt] = true;
+  return GEMM_SM100_OK;
+}
+
+template <int kCfgIndex, bool kIsBf16>
+int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceState& st, cudaStream_t stream,
+                  int* cuda_error_out) {
+  constexpr ConfigInfo ci = kConfigs[kCfgIndex];
+  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  constexpr int dt = kIsBf16 ? 0 : 1;
+  int rc = ensure_config<kCfgIndex, kIsBf16>(st, cuda_error_out);
+  if (rc) return rc;
+  // The instrumented instantiation runs only while a trace buffer (of this device) or an
+  // experiment flag is set.
+  const TraceBuffer trace = trace_for_device(st.device);
+  const bool debug = trace.ptr != nullptr || g_opt_debug_flags.load() != 0;
+  auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
+  if constexpr (has_split_k(kCfgIndex)) {
+    if (plan.split_k) kernel = gemm_tn_kernel<Cfg, false, true>;
+  }
+  cudaError_t e;
+
+  TileParams tp = base_tile_params<Cfg>(p, st);
+  tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
+  const long k_order = g_opt_k_rotate.load();
+  tp.k_rotate = k_order == 2 ? 2 : ((k_order == 1 || (k_order < 0 && tp.m_tiles == 1 && !plan.split_k)) ? 1 : 0);
+  if (plan.split_k) {
+    tp.sk_flags = static_cast<unsigned int*>(workspace);
+    tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
+    tp.sk_rows = plan.partial_rows;
+    tp.sk_factor = plan.split_factor;
+    e = cudaMemsetAsync(tp.sk_flags, 0, plan.flag_bytes, stream);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  }
+
+  CUtensorMap map_a, map_b, map_c;
+  rc = encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  if (rc) return rc;
+  rc = encode_2d_cached(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
+  if (rc) return rc;
+  rc = encode_2d_cached(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
+  if (rc) return rc;
+
+  long ctas = plan.ctas;
+  if (ctas > st.max_ctas[kCfgIndex][dt]) {
+    // Fewer co-resident CTAs than SMs (never seen on B200).  The K-split schedule needs the
+    // grid it was planned for, because the workspace is indexed by CTA.
+    if (plan.split_k) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
+    ctas = st.max_ctas[kCfgIndex][dt];
+  }
+  if (trace.ptr && trace.bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
+    tp.trace = trace.ptr;
+
+  e = launch_kernel<Cfg>(kernel, ctas, stream, map_a, map_b, map_c, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -472,47 +595,33 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
                   int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
   using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
-  auto kernel = gemm_tn_fanout_kernel<Cfg>;
+  static_assert(has_fanout(kCfgIndex), "no store-to-every-output variant of this configuration");
   constexpr int dt = kIsBf16 ? 0 : 1;
-  cudaError_t e;
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (!st.fanout_attr_set[kCfgIndex][dt]) {
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-      st.fanout_attr_set[kCfgIndex][dt] = true;
-    }
-  }
-  const TileParams tp = base_tile_params<Cfg>(p, st);
+  int rc = ensure_config<kCfgIndex, kIsBf16>(st, cuda_error_out);
+  if (rc) return rc;
+  const TraceBuffer trace = trace_for_device(st.device);
+  auto kernel = trace.ptr ? gemm_tn_fanout_kernel<Cfg, true> : gemm_tn_fanout_kernel<Cfg, false>;
+  TileParams tp = base_tile_params<Cfg>(p, st);
 
   CUtensorMap map_a, map_b;
   OutputMaps out;
   std::memset(&out, 0, sizeof(out));
-  int rc = encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  rc = encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
   if (rc) return rc;
-  rc = encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
+  rc = encode_2d_cached(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
   if (rc) return rc;
   for (int d = 0; d < num_outputs; ++d) {
-    rc = encode_2d(&out.maps[d], outputs[d], p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
+    rc = encode_2d_cached(&out.maps[d], outputs[d], p.dtype, p.M, p.N, p.ldc, 32, cuda_error_out);
     if (rc) return rc;
   }
   long ctas = static_cast<long>(tp.m_tiles) * tp.n_tiles * Cfg::kCtaGroup;
   const long cap = grid_cap(ci, st.sm_count);
   if (ctas > cap) ctas = cap;
+  if (ctas > st.max_ctas[kCfgIndex][dt]) ctas = st.max_ctas[kCfgIndex][dt];
+  if (trace.ptr && trace.bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
+    tp.trace = trace.ptr;
 
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(ctas));
-  cfg.blockDim = dim3(Cfg::kThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
-  attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = Cfg::kCtaGroup;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
-  cfg.attrs = attrs;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, out, num_outputs, tp);
+  cudaError_t e = launch_kernel<Cfg>(kernel, ctas, stream, map_a, map_b, out, num_outputs, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -523,44 +632,22 @@ template <int kCfgIndex, bool kIsBf16>
 int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
   using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  static_assert(has_layouts(kCfgIndex), "no layout variants of this configuration");
   auto kernel = p.a_is_km ? (p.b_is_kn ? gemm_layout_kernel<Cfg, true, true> : gemm_layout_kernel<Cfg, true, false>)
                           : (p.b_is_kn ? gemm_layout_kernel<Cfg, false, true> : gemm_layout_kernel<Cfg, false, false>);
-  constexpr int dt = kIsBf16 ? 0 : 1;
-  cudaError_t e;
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (!st.nn_attr_set[kCfgIndex][dt]) {
-      for (auto k : {gemm_layout_kernel<Cfg, true, true>, gemm_layout_kernel<Cfg, true, false>,
-                     gemm_layout_kernel<Cfg, false, true>, gemm_layout_kernel<Cfg, false, false>}) {
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
-      }
-      st.nn_attr_set[kCfgIndex][dt] = true;
-    }
-  }
+  int rc = ensure_config<kCfgIndex, kIsBf16>(st, cuda_error_out);
+  if (rc) return rc;
   const TileParams tp = base_tile_params<Cfg>(p, st);
   CUtensorMap map_a, map_b, map_c;
-  int rc = p.a_is_km ? encode_2d(&map_a, p.A, p.dtype, p.K, p.M, p.lda, 64, cuda_error_out)   // K rows of M columns
-                     : encode_2d(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  rc = p.a_is_km ? encode_2d_cached(&map_a, p.A, p.dtype, p.K, p.M, p.lda, 64, cuda_error_out)   // K rows of M columns
+                 : encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
   if (rc) return rc;
-  rc = p.b_is_kn ? encode_2d(&map_b, p.B, p.dtype, p.K, p.N, p.ldb, 64, cuda_error_out)       // K rows of N columns
-                 : encode_2d(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
+  rc = p.b_is_kn ? encode_2d_cached(&map_b, p.B, p.dtype, p.K, p.N, p.ldb, 64, cuda_error_out)   // K rows of N columns
+                 : encode_2d_cached(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
   if (rc) return rc;
-  rc = encode_2d(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
+  rc = encode_2d_cached(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
   if (rc) return rc;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(plan.ctas));
-  cfg.blockDim = dim3(Cfg::kThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
-  attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = Cfg::kCtaGroup;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
-  cfg.attrs = attrs;
-  cfg.numAttrs = Cfg::kCtaGroup == 2 ? 1 : 0;
-  e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, tp);
+  const cudaError_t e = launch_kernel<Cfg>(kernel, plan.ctas, stream, map_a, map_b, map_c, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -587,6 +674,7 @@ int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cuda
     case 5: return launch_config<5, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 6: return launch_config<6, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 7: return launch_config<7, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 8: return launch_config<8, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }
@@ -625,14 +713,14 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
     rc = get_encoder(cuda_error_out);
     if (rc != GEMM_SM100_OK) return rc;
   }
-  Plan plan = make_plan(M, N, K, st->sm_count);
+  Plan plan = plan_for(M, N, K, st->sm_count);
   if (plan.split_k) {
     if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
         workspace_bytes < plan.flag_bytes + plan.partial_bytes) {
       // A K-split the caller asked for needs its workspace; one the planner chose by itself is
       // only an optimisation: without the memory the problem runs as whole tiles.
       if (g_opt_split_k > 0) return GEMM_SM100_ERR_WORKSPACE;
-      plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false);
+      plan = plan_for(M, N, K, st->sm_count, /*allow_split=*/false);
     }
   }
   if (dtype == GEMM_SM100_BF16) return dispatch<true>(plan, p, workspace, *st, stream, cuda_error_out);
@@ -716,13 +804,21 @@ int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int
     if (rc != GEMM_SM100_OK) return rc;
   }
   Problem p{A, B, outputs[0], M, N, K, lda, ldb, ldc, dtype};
-  // Pair-tile configurations only; the same wave model as the plain GEMM picks between them.
+  // Pair-tile configurations only.  The wave model of the plain GEMM, with what the epilogue's
+  // extra stores cost added to the tile boundary: the 256 x 512 tile fills TMEM, so the time its
+  // epilogue needs to push every 64-column chunk through one staging buffer per warp to
+  // `num_outputs` destinations (all but one of them across NVLink in the multi-GPU use) is
+  // exposed before the next tile's first MMA; the 256 x 256 tile drains one accumulator slot
+  // while the tensor pipe fills the other, with two staging buffers per warp, and hides it.
+  // Measured on 8 GPUs (32768 x 4096 x 32768 slabs): 16 % of the step with the wide tile.  About
+  // one K block per output beyond the first, fitted to that.
   const long slots = st->sm_count / 2;
   const double k_blocks = static_cast<double>(ceil_div(K, 64L));
   const double cost0 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 256L), slots)) * 256 *
                        (k_blocks + kTileBoundaryKBlocks[0]) / kConfigRate[0];
   const double cost1 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 512L), slots)) * 512 *
-                       (k_blocks + kTileBoundaryKBlocks[1]) / kConfigRate[1];
+                       (k_blocks + kTileBoundaryKBlocks[1] + kFanoutKBlocksPerOutput * (num_outputs - 1)) /
+                       kConfigRate[1];
   const bool wide = g_opt_tile_config == 1 || (g_opt_tile_config != 0 && cost1 <= cost0);
   if (dtype == GEMM_SM100_BF16)
     return wide ? launch_fanout<1, true>(p, outputs, num_outputs, *st, stream, cuda_error_out)
@@ -767,7 +863,7 @@ int gemm_sm100_gemm_scaled(const void* A, const void* B, void* C, int M, int N, 
     rc = get_encoder(cuda_error_out);
     if (rc != GEMM_SM100_OK) return rc;
   }
-  Plan plan = make_plan(M, N, K, st->sm_count, /*allow_split=*/false, /*config_limit=*/4);
+  Plan plan = plan_for(M, N, K, st->sm_count, /*allow_split=*/false, /*config_limit=*/4);
   if (plan.config > 3) plan = Plan{};       // (a forced configuration without such a variant)
   if (plan.ctas == 0) {
     const long tiles = ceil_div(M, 256L) * ceil_div(N, 256L);
@@ -798,7 +894,7 @@ size_t gemm_sm100_static_scratch_capacity(void) { return kStaticScratchBytes; }
 size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype) {
   (void)dtype;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const Plan plan = make_plan(M, N, K, current_sm_count());
+  const Plan plan = plan_for(M, N, K, current_sm_count());
   return plan.split_k ? plan.flag_bytes + plan.partial_bytes : 0;
 }
 
@@ -835,6 +931,7 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out) {
 int gemm_sm100_set_option(const char* name, long value) {
   if (!name) return GEMM_SM100_ERR_NULL_POINTER;
   std::lock_guard<std::mutex> lock(g_mutex);
+  g_opt_generation.fetch_add(1, std::memory_order_acq_rel);   // cached plans depend on the options
   if (std::strcmp(name, "tile_config") == 0) {
     if (value < -1 || value >= kNumConfigs) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_tile_config = value;
@@ -851,7 +948,7 @@ int gemm_sm100_set_option(const char* name, long value) {
     return GEMM_SM100_OK;
   }
   if (std::strcmp(name, "k_rotate") == 0) {
-    if (value < -1 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    if (value < -1 || value > 2) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_k_rotate = value;
     return GEMM_SM100_OK;
   }
@@ -874,10 +971,22 @@ int gemm_sm100_set_option(const char* name, long value) {
 }
 
 int gemm_sm100_set_trace_buffer(void* device_buffer, size_t bytes) {
-  std::lock_guard<std::mutex> lock(g_mutex);
   if (device_buffer != nullptr && (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) return GEMM_SM100_ERR_BAD_ALIGNMENT;
-  g_trace_ptr = static_cast<unsigned long long*>(device_buffer);
-  g_trace_bytes = device_buffer ? bytes : 0;
+  int device = -1;
+  if (device_buffer != nullptr) {
+    // The buffer belongs to one device: only launches on that device may write to it.
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, device_buffer) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+      (void)cudaGetLastError();
+      return GEMM_SM100_ERR_BAD_OPTION;
+    }
+    device = attr.device;
+  }
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_trace.ptr = static_cast<unsigned long long*>(device_buffer);
+  g_trace.bytes = device_buffer ? bytes : 0;
+  g_trace.device = device;
+  g_trace_on.store(device_buffer != nullptr, std::memory_order_release);
   return GEMM_SM100_OK;
 }
 
@@ -885,15 +994,16 @@ int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes) {
   if (!buf || buf_bytes == 0) return GEMM_SM100_ERR_NULL_POINTER;
   if (index < 0 || index >= kNumConfigs) return GEMM_SM100_ERR_BAD_OPTION;
   const ConfigInfo& c = kConfigs[index];
+  const int tmem_cols = 2 * c.mma_n <= 128 ? 128 : (2 * c.mma_n <= 256 ? 256 : 512);
   std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d epilogue_warps=%d",
-                c.cta_group, 128 * c.cta_group, c.mma_n * c.halves, c.stages, 2 * c.mma_n, c.epi_warps);
+                c.cta_group, 128 * c.cta_group, c.mma_n * c.halves, c.stages, tmem_cols, c.epi_warps);
   return GEMM_SM100_OK;
 }
 
 int gemm_sm100_select_config(int M, int N, int K, int dtype) {
   (void)dtype;
   if (M <= 0 || N <= 0 || K <= 0) return -1;
-  return make_plan(M, N, K, current_sm_count()).config;
+  return plan_for(M, N, K, current_sm_count()).config;
 }
 
 const char* gemm_sm100_error_string(int code) {
@@ -916,3 +1026,39 @@ const char* gemm_sm100_error_string(int code) {
 }
 
 }  // extern "C"
+
+namespace {
+
+template <int kCfgIndex>
+int ensure_both_dtypes(DeviceState& st, int* cuda_error_out) {
+  const int rc = ensure_config<kCfgIndex, true>(st, cuda_error_out);
+  return rc ? rc : ensure_config<kCfgIndex, false>(st, cuda_error_out);
+}
+
+template <int... kIndices>
+int ensure_all(DeviceState& st, int* cuda_error_out, std::integer_sequence<int, kIndices...>) {
+  int rc = GEMM_SM100_OK;
+  (void)((rc = ensure_both_dtypes<kIndices>(st, cuda_error_out), rc == GEMM_SM100_OK) && ...);
+  return rc;
+}
+
+}  // namespace
+
+extern "C" int gemm_sm100_init(int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc = device_state(&st, cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    rc = get_encoder(cuda_error_out);
+    if (rc != GEMM_SM100_OK) return rc;
+    if (st->static_scratch == nullptr) {
+      void* ptr = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+      st->static_scratch = ptr;
+    }
+  }
+  return ensure_all(*st, cuda_error_out, std::make_integer_sequence<int, kNumConfigs>{});
+}

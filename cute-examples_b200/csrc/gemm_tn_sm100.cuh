@@ -69,9 +69,12 @@ struct TileParams {
   int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
   int sk_factor;                   // <= 1: contiguous ranges; > 1: every tile cut into this many equal K ranges
                                    // (then one partial tile per unit and CTA of the pair, one counter per tile and CTA)
-  // Start every tile's K loop at a different K block (wrapping around).  Used when each B tile is
-  // read exactly once (a single tile row, the memory-bound small-M case): the CTAs then stream
-  // different column offsets at any moment, which spreads the requests over the DRAM channels.
+  // Order in which a tile's K blocks are loaded (the sum does not depend on it beyond rounding):
+  // 0 ascending.  1 ("rotate"): every tile starts at a different K block and wraps around, so CTAs
+  // that each stream their own B tile hit different column offsets at any moment.  2
+  // ("serpentine"): every other tile of a CTA runs K backwards, so the operand panel that
+  // consecutive tiles of the rasterisation share is re-read most-recently-loaded first, while
+  // its tail end is still in L2.
   int k_rotate;
   // Optional epilogue scaling (kernels instantiated with kScaled only): C = alpha * acc + beta * C.
   float alpha, beta;
@@ -131,14 +134,18 @@ struct GemmConfig {
   static constexpr int kEpiWarpBuf = 32 * kEpiCols * 2;         // one warp, one chunk: 4 KiB
   static constexpr int kEpiBufs = 8 / kEpiWarps;                // staging buffers per warp
   static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiWarpBuf;   // 32 KiB
-  static constexpr int kTmemCols = 2 * kMmaN;                   // two accumulator slots
+  // Two accumulator slots.  TMEM is allocated in powers of two (32..512 columns); the slots sit
+  // half an allocation apart, so a 192-column accumulator leaves 64 unused columns behind it.
+  static constexpr int kTmemCols = 2 * kMmaN <= 128 ? 128 : (2 * kMmaN <= 256 ? 256 : 512);
+  static constexpr int kSlotCols = kTmemCols / 2;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kBarrierBytes;
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
   static_assert(kHalves == 1 || kHalves == 2, "halves");
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps");
   static_assert(kMmaN % 64 == 0 && kMmaN >= 64 && kMmaN <= 256, "MMA N");
-  static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns: power of two");
+  static_assert(kMmaN <= kSlotCols, "an accumulator must fit its slot");
+  static_assert(kCtaGroup == 1 || kMmaN % 32 == 0, "pair MMA: each CTA supplies N / 2 rows of B, a multiple of 16");
   static_assert(kBHalfBytes % 1024 == 0, "B tile must keep 1024-byte swizzle alignment");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
@@ -430,8 +437,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
       Segment seg;
       bool have = work.next(seg);
-      int kb = seg.kb0, row_a = 0, row_b = 0, rot = 0;
-      bool seg_start = true;
+      int kb = seg.kb0, row_a = 0, row_b = 0, rot = 0, tiles_done = 0;
+      bool seg_start = true, backwards = false;
       bool ok = true;
       long long stall = 0;
       while (have && ok) {
@@ -443,7 +450,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             tile_coords(seg.tile, p, m_tile, n_tile);
             row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
             row_b = n_tile * Cfg::kBlockN + (int)cta_rank * Cfg::kBRows;
-            rot = p.k_rotate ? (int)(((long long)seg.tile * k_blocks) / num_tiles) : 0;
+            rot = p.k_rotate == 1 ? (int)(((long long)seg.tile * k_blocks) / num_tiles) : 0;
+            backwards = !kSplitK && p.k_rotate == 2 && (tiles_done & 1);
+            ++tiles_done;
             seg_start = false;
           }
           long long t0 = 0;
@@ -456,6 +465,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             if (trace) stall += clock64() - t0;
           int kb_phys = kb + rot;                  // which K block this step loads (order is free)
           if (kb_phys >= k_blocks) kb_phys -= k_blocks;
+          if (backwards) kb_phys = k_blocks - 1 - kb;
           const int x = kb_phys * Cfg::kBlockK;
           if (issuer) {
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
@@ -563,7 +573,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
                 if (trace) stall_acc += clock64() - ta;
               tc_fence_after_sync();
             }
-            const uint32_t tmem_d = tmem_base + slot * Cfg::kMmaN;
+            const uint32_t tmem_d = tmem_base + slot * Cfg::kSlotCols;
             // descriptor address fields are in 16-byte units; +2 per 16-element K step (32 bytes
             // inside the 128-byte swizzle row)
             const uint64_t da = da0 + (uint64_t)((s * Cfg::kABytes) >> 4);
@@ -675,7 +685,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
         if constexpr (kDebug)
           if (trace) stall += clock64() - te;
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + slot * Cfg::kMmaN;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + slot * Cfg::kSlotCols;
         // Everything that happens to one 32-row x 64-column chunk once it sits in registers.
         auto finish_chunk = [&](const int c, uint32_t (&v0)[32], uint32_t (&v1)[32]) {
           if constexpr (kSplitK) {
@@ -983,11 +993,11 @@ struct OutputMaps {
   CUtensorMap maps[kMaxOutputs];
 };
 
-template <class Cfg>
+template <class Cfg, bool kDebug = false>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tn_fanout_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ OutputMaps outputs, const int num_outputs, const TileParams p) {
-  gemm_tn_body<Cfg, false, false>(tmap_a, tmap_b, outputs.maps, num_outputs, p);
+  gemm_tn_body<Cfg, kDebug, false>(tmap_a, tmap_b, outputs.maps, num_outputs, p);
 }
 
 }  // namespace gemm_sm100

@@ -8,7 +8,10 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
+#include <map>
+#include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/gemm_sm100.h"
@@ -29,6 +32,24 @@ int dtype_code(const torch::Tensor& t) {
   if (t.scalar_type() == torch::kFloat16) return GEMM_SM100_FP16;
   TORCH_CHECK(false, "Both tensors must be of type bfloat16 or float16");
   return -1;
+}
+
+// K-split scratch memory, kept between calls: one buffer per (device, stream), grown on demand.
+// A torch::empty per call costs microseconds, which is a large part of the few-tile, long-K
+// GEMMs that use the schedule.  Keyed by stream because two GEMMs on different streams may run at
+// the same time and must not share partial tiles; calls on one stream are ordered.  The
+// buffers come from torch's caching allocator and live until the process ends.
+void* kept_workspace(const c10::Device& device, cudaStream_t stream, size_t bytes) {
+  static std::mutex mutex;
+  static std::map<std::pair<int, cudaStream_t>, torch::Tensor> kept;
+  std::lock_guard<std::mutex> lock(mutex);
+  torch::Tensor& t = kept[{static_cast<int>(device.index()), stream}];
+  if (!t.defined() || static_cast<size_t>(t.numel()) < bytes) {
+    // the old buffer (if any) goes back to the allocator, which keeps it alive for the work
+    // already queued on the stream it was allocated on
+    t = torch::empty({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(device));
+  }
+  return t.data_ptr();
 }
 
 }  // namespace
@@ -61,15 +82,9 @@ torch::Tensor gemm_tn_test(const torch::Tensor A, const torch::Tensor B, torch::
   if (M == 0 || N == 0) return C;
 
   c10::cuda::CUDAGuard guard(A.device());
-  const size_t ws_bytes = gemm_sm100_workspace_bytes(M, N, K, dtype);
-  torch::Tensor workspace;
-  void* ws_ptr = nullptr;
-  if (ws_bytes > 0) {
-    workspace = torch::empty({static_cast<int64_t>(ws_bytes)},
-                             torch::TensorOptions().dtype(torch::kUInt8).device(A.device()));
-    ws_ptr = workspace.data_ptr();
-  }
   cudaStream_t stream = c10::cuda::getCurrentCUDAStream(A.device().index()).stream();
+  const size_t ws_bytes = gemm_sm100_workspace_bytes(M, N, K, dtype);
+  void* const ws_ptr = ws_bytes > 0 ? kept_workspace(A.device(), stream, ws_bytes) : nullptr;
   const long ldc = M > 1 ? static_cast<long>(C.stride(0)) : static_cast<long>(N);
   const long lda = M > 1 ? static_cast<long>(A.stride(0)) : static_cast<long>(K);
   const long ldb = N > 1 ? static_cast<long>(B.stride(0)) : static_cast<long>(K);
@@ -189,6 +204,12 @@ void set_trace_buffer(const c10::optional<torch::Tensor>& buffer) {
   raise_for(gemm_sm100_set_trace_buffer(t.data_ptr(), static_cast<size_t>(t.numel()) * 8), 0, "set_trace_buffer");
 }
 
+// One-time set-up of the current device (see gemm_sm100_init); optional.
+void init() {
+  int cuda_error = 0;
+  raise_for(gemm_sm100_init(&cuda_error), cuda_error, "init");
+}
+
 void set_option(const std::string& name, long value) {
   raise_for(gemm_sm100_set_option(name.c_str(), value), 0, "set_option");
 }
@@ -212,6 +233,7 @@ PYBIND11_MODULE(_C, m) {
         pybind11::arg("A"), pybind11::arg("B"), pybind11::arg("output_ptrs"), pybind11::arg("ldc"));
   m.def("device_status", &device_status,
         "Synchronise the current device and raise if a GEMM kernel reported a failed wait");
+  m.def("init", &init, "One-time set-up of the current device; call before capturing a CUDA graph");
   m.def("set_option", &set_option, pybind11::arg("name"), pybind11::arg("value"));
   m.def("set_trace_buffer", &set_trace_buffer, pybind11::arg("buffer"));
   m.def("describe_config", &describe_config, pybind11::arg("index"));

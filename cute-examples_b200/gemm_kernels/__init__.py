@@ -30,6 +30,7 @@ import torch as _torch
 gemm_tn_test = _C.gemm_tn_test
 gemm_tn_fanout = _C.gemm_tn_fanout
 device_status = _C.device_status
+init = _C.init
 set_option = _C.set_option
 set_trace_buffer = _C.set_trace_buffer
 describe_config = _C.describe_config
@@ -100,10 +101,12 @@ class HostGemm:
 
     The whole of B is uploaded first; A is uploaded in row panels, each panel's GEMM starts as
     soon as its rows have arrived, and each finished panel of C goes back to the host while the
-    next panel of A is still coming in (PCIe carries both directions at once).  Device buffers
-    and streams are created once and reused; `__call__` returns after the last byte of C has
-    reached the host.  The reference has no host-memory path: its callers create operands on
-    the device (kernels/tests/gemm_test.py:23-28).
+    next panel of A is still coming in (PCIe carries both directions at once).  The upload link
+    is busy from the first byte to the last, so the step takes the upload time plus what follows
+    the last byte of A: the last panel's GEMM and download.  The last of the `panels` panels is
+    therefore cut once more into quarters.  Device buffers and streams are created once and
+    reused; `__call__` returns after the last byte of C has reached the host.  The reference has
+    no host-memory path: its callers create operands on the device (kernels/tests/gemm_test.py:23-28).
     """
 
     def __init__(self, M: int, N: int, K: int, dtype=_torch.bfloat16, device="cuda", panels: int = 8):
@@ -111,6 +114,15 @@ class HostGemm:
         self.device = _torch.device(device)
         rows = -(-M // max(1, panels))
         self.panel_rows = max(256, -(-rows // 256) * 256) if M >= 256 else M
+        # row ranges: equal panels, the last one in quarters (multiples of 256 rows where possible)
+        self.ranges = []
+        for r0 in range(0, M, self.panel_rows):
+            r1 = min(M, r0 + self.panel_rows)
+            if r1 == M and r1 - r0 >= 1024:
+                q = -(-(r1 - r0) // 4 // 256) * 256
+                self.ranges += [(a, min(M, a + q)) for a in range(r0, r1, q)]
+            else:
+                self.ranges.append((r0, r1))
         self.A = _torch.empty((M, K), dtype=dtype, device=self.device)
         self.B = _torch.empty((N, K), dtype=dtype, device=self.device)
         self.C = _torch.empty((M, N), dtype=dtype, device=self.device)
@@ -126,8 +138,7 @@ class HostGemm:
         self.d2h.wait_stream(compute)
         with _torch.cuda.stream(self.h2d):
             self.B.copy_(B_host, non_blocking=True)
-        for r0 in range(0, self.M, self.panel_rows):
-            r1 = min(self.M, r0 + self.panel_rows)
+        for r0, r1 in self.ranges:
             with _torch.cuda.stream(self.h2d):
                 self.A[r0:r1].copy_(A_host[r0:r1], non_blocking=True)
                 arrived = _torch.cuda.Event()
@@ -148,5 +159,5 @@ from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, sh
 
 __all__ = [
     "gemm_tn_test", "gemm_tn", "gemm_nn", "gemm", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
-    "set_option", "set_trace_buffer", "trace_launch", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
+    "init", "set_option", "set_trace_buffer", "trace_launch", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

@@ -144,31 +144,47 @@ def fanout_pointers(buffer_ptrs, rank: int, column_offset: int, element_size: in
 class FusedNSplit:
     """Column-sharded GEMM with the all-gather of C folded into the GEMM epilogue.
 
-    Every rank owns a full ``C[M, N]`` in symmetric memory (same allocation on every GPU, mapped
-    into every process).  Rank g computes its column slab ``A @ B_g.T`` once and its epilogue
+    Every rank owns full ``C[M, N]`` buffers in symmetric memory (same allocation on every GPU,
+    mapped into every process).  Rank g computes its column slab ``A @ B_g.T`` once and its epilogue
     stores every finished tile into all G copies of C (one TMA store per GPU per tile: the local
     one and G-1 over NVLink), at column offset ``g * N/G``.  No staging slab, no NCCL all-gather,
-    no re-stride copy; one cross-GPU barrier before the step (nobody still reads the previous C)
-    and one after it (everybody's stores have landed).  Peer memory is only ever written, never
-    loaded from.
+    no re-stride copy.  Peer memory is only ever written, never loaded from.
+
+    Synchronisation: ONE cross-GPU barrier per call, after the GEMM (everybody's stores have
+    landed).  The barrier that would have to precede the GEMM (nobody still reads the C that is
+    about to be overwritten) is made unnecessary by alternating between ``buffers`` = 2 copies of
+    C: call t writes copy t % 2; a peer can start writing into this rank's copy t % 2 only after it
+    has passed the barrier of call t-1, which this rank enters, in stream order, after its own
+    call t-1 and therefore after everything it enqueued to read the result of call t-2.
+    So: the tensor a call returns stays valid until the call after the next one, and must be
+    read by work enqueued (on the calling stream) before this rank's next call.  With
+    ``buffers=1`` there is one copy of C and two barriers per call.
     """
 
-    def __init__(self, M: int, N: int, dtype: torch.dtype, device, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, M: int, N: int, dtype: torch.dtype, device, group: Optional[dist.ProcessGroup] = None,
+                 buffers: int = 2):
         import torch.distributed._symmetric_memory as symm_mem
 
+        if buffers not in (1, 2):
+            raise ValueError("buffers must be 1 or 2")
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.M, self.N = M, N
         self.lo, self.hi = shard_rows(N, self.world, self.rank)
-        self.C = symm_mem.empty((M, N), dtype=dtype, device=device)
-        self.handle = symm_mem.rendezvous(self.C, self.group)
+        if self.world > 8:
+            raise ValueError("the fused exchange stores to at most 8 GPUs")
+        self.storage = symm_mem.empty((buffers, M, N), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.storage, self.group)
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         if len(ptrs) != self.world:
             raise RuntimeError("symmetric memory rendezvous returned an unexpected number of buffers")
-        if self.world > 8:
-            raise ValueError("the fused exchange stores to at most 8 GPUs")
-        self.output_ptrs = fanout_pointers(ptrs, self.rank, self.lo, self.C.element_size())
+        esize = self.storage.element_size()
+        self.copies = [self.storage[i] for i in range(buffers)]
+        self.output_ptrs = [fanout_pointers([p + i * M * N * esize for p in ptrs], self.rank, self.lo, esize)
+                            for i in range(buffers)]
+        self.calls = 0
+        self.C = self.copies[0]
 
     def __call__(self, A: torch.Tensor, B_shard: torch.Tensor) -> torch.Tensor:
         from . import gemm_tn_fanout
@@ -176,9 +192,13 @@ class FusedNSplit:
         if tuple(A.shape) != (self.M, B_shard.shape[1]) or B_shard.shape[0] != self.hi - self.lo:
             raise ValueError(f"expected A [{self.M}, K] and B shard [{self.hi - self.lo}, K], got "
                              f"{tuple(A.shape)} and {tuple(B_shard.shape)}")
-        self.handle.barrier(channel=0)
-        gemm_tn_fanout(A, B_shard, self.output_ptrs, self.N)
+        which = self.calls % len(self.copies)
+        self.calls += 1
+        if len(self.copies) == 1:
+            self.handle.barrier(channel=0)
+        gemm_tn_fanout(A, B_shard, self.output_ptrs[which], self.N)
         self.handle.barrier(channel=1)
+        self.C = self.copies[which]
         return self.C
 
 

@@ -11,6 +11,20 @@
  * All pointers are device pointers on the CURRENT CUDA device unless stated otherwise.
  * Nothing here allocates device memory and nothing calls exit(): every failure is a
  * return code (the reference prints and exits on a CUDA error, gemm_test.cu:78,86).
+ *
+ * First use and stream capture.  The first launch of a tile configuration on a device sets
+ * function attributes and queries occupancy (host-side calls, no device work and no
+ * synchronisation).  A host that captures CUDA graphs should call gemm_sm100_init() once per
+ * device before its first capture, which does all of that up front.
+ *
+ * Co-residency.  The K-split schedules (gemm_sm100_workspace_bytes() > 0, or the "split_k"
+ * option, or gemm_sm100_tn_static_scratch) let CTAs wait for partial sums of other CTAs of the
+ * same grid, so the whole grid must be resident at once.  The grid is sized from the device's SM
+ * count; a host that gives this library only part of the SMs (an SM-limited or "green" context,
+ * a long-running kernel on another stream) should set the option "split_k" to 0, or "max_ctas"
+ * to the SMs it really has.  If such a wait runs out ("timeout_ms") the kernel returns with C
+ * partly unwritten and the only signal is the status word: read it with
+ * gemm_sm100_device_status().
  */
 #ifndef GEMM_SM100_H_
 #define GEMM_SM100_H_
@@ -68,9 +82,10 @@ int gemm_sm100_nn(const void* A, const void* B, void* C, int M, int N, int K, lo
 
 /* All four operand layouts behind one call: A as [M,K] (a_is_km = 0) or [K,M] (1, pitch
  * lda >= M), B as [N,K] (b_is_kn = 0) or [K,N] (1, pitch ldb >= N).  (0,0) is gemm_sm100_tn
- * without a workspace (so shapes for which gemm_sm100_workspace_bytes is non-zero are refused
- * there: call gemm_sm100_tn for those), (0,1) is gemm_sm100_nn.  The [K,*] forms are loaded as
- * MN-major operands; whole tiles only.  No reference counterpart (TN only). */
+ * without a workspace: a K-split the library would have chosen by itself then runs as whole
+ * tiles (call gemm_sm100_tn with a workspace to get the split); (0,1) is gemm_sm100_nn.  The
+ * [K,*] forms are loaded as MN-major operands; whole tiles only.  No reference counterpart (TN
+ * only). */
 int gemm_sm100_gemm(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                     int dtype, int a_is_km, int b_is_kn, void* cuda_stream, int* cuda_error_out);
 
@@ -142,16 +157,27 @@ int gemm_sm100_num_sms(void);
  * (gemm_test.cu:86), which synchronises and exits the process on error. */
 int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
 
-/* Tuning / test knobs, process-wide.  Names: "tile_config" (-1 = choose automatically,
- * otherwise an index reported by gemm_sm100_describe_config), "timeout_ms" (bound of each
- * device-side wait, default 2000), "max_ctas" (0 = all SMs; caps the persistent grid),
- * "split_k" (-1 = automatic, 0 = never, 1 = contiguous K ranges, one per CTA or pair, whenever the
- * chosen configuration has a K-split variant; 2..8 = every tile cut into that many equal K ranges
- * with the reduction spread over the contributors, on the 256 x 256 and 128 x 256 tiles), "group_m" (0 = default; tile rows per rasterisation group), "k_rotate" (0 = off, the default; 1 = on; -1 = on for a single tile row:
- * start each tile's K loop at a different K block).  Set them before
- * asking gemm_sm100_workspace_bytes, which depends on them.  The environment variables
- * GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M, GEMM_SM100_MAX_CTAS and
- * GEMM_SM100_TIMEOUT_MS give the initial values when the library is loaded.
+/* Tuning / test knobs, process-wide.  Set them before asking gemm_sm100_workspace_bytes, which
+ * depends on them.
+ *   "tile_config"  -1 = choose automatically (default), otherwise an index reported by
+ *                  gemm_sm100_describe_config.
+ *   "timeout_ms"   bound of each device-side wait, 1..60000, default 2000.
+ *   "max_ctas"     0 = all SMs (default); otherwise caps the persistent grid.
+ *   "split_k"      -1 = automatic (default); 0 = never; 1 = contiguous K ranges, one per CTA or
+ *                  pair, whenever the chosen configuration has a K-split variant; 2..8 = every
+ *                  tile cut into that many equal K ranges with the reduction spread over the
+ *                  contributors (256 x 256 and 128 x 256 tiles).
+ *   "group_m"      0 = default; tile rows per rasterisation group.
+ *   "k_rotate"     order of a tile's K blocks: 0 = ascending (default); 1 = every tile starts at a
+ *                  different K block and wraps; -1 = that, for a single tile row only; 2 = every
+ *                  other tile of a CTA runs K backwards (re-reads the shared operand panel
+ *                  newest-first).
+ *   "debug_flags"  EXPERIMENTS ONLY, results are garbage while it is non-zero: bit 0 skips the
+ *                  operand loads, bit 1 the stores of C, bit 2 the MMAs (pure issue-rate and
+ *                  load-rate measurements of tests/trace_report.py).  Default 0.
+ * The environment variables GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M,
+ * GEMM_SM100_MAX_CTAS and GEMM_SM100_TIMEOUT_MS give the initial values when the library is
+ * loaded ("debug_flags" has no variable on purpose).
  * The reference's equivalents are compile-time constants (gemm.cuh:420-451). */
 int gemm_sm100_set_option(const char* name, long value);
 
@@ -163,12 +189,23 @@ int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes);
  * device (negative on error). */
 int gemm_sm100_select_config(int M, int N, int K, int dtype);
 
-/* Profiling aid.  While a device buffer is registered, every launch whose grid fits
+/* One-time set-up of the current device, optional: looks up the driver's tensor-map encoder and
+ * the library's device variables, sets the shared-memory limit of every kernel instantiation
+ * and queries how many CTAs of each are co-resident.  Idempotent and thread-safe; issues no
+ * device work.  Every launching entry point does the part it needs on first use; call this
+ * once per device before capturing a stream.  No reference counterpart (the reference sets
+ * its one kernel's attribute on every call, gemm_test.cu:74-78). */
+int gemm_sm100_init(int* cuda_error_out);
+
+/* Profiling aid.  While a device buffer is registered, every launch ON THE DEVICE THAT OWNS THE
+ * BUFFER whose grid fits
  * (grid CTAs x 16 x 8 bytes <= bytes) writes one 16-word record per CTA: clock64 stamps of
  * kernel entry, set-up done, first operand stage, last MMA issued, last load issued, epilogue
  * done, exit; cycles each role spent waiting (MMA on operand stages [3] and on a free
  * accumulator [4], producer on free ring slots [6], epilogue on accumulators [8]); tiles
  * processed [11]; %globaltimer at entry [12] and exit [13].  NULL switches tracing off.
+ * Launches on other devices ignore the buffer.  The caller keeps the memory alive until it
+ * has switched tracing off; a pointer that is not device memory is refused.
  * The reference has no tracing in code; its profiler.py is a bare launch for Nsight
  * (kernels/tests/profiler.py:1-12). */
 int gemm_sm100_set_trace_buffer(void* device_buffer, size_t bytes);

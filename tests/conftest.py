@@ -75,6 +75,8 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_selftest_wait_timeout.restype = I
     lib.gemm_sm100_set_trace_buffer.argtypes = [P, Z]
     lib.gemm_sm100_set_trace_buffer.restype = I
+    lib.gemm_sm100_init.argtypes = [ctypes.POINTER(I)]
+    lib.gemm_sm100_init.restype = I
     lib.gemm_sm100_error_string.argtypes = [I]
     lib.gemm_sm100_error_string.restype = ctypes.c_char_p
     return lib

@@ -20,7 +20,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 DT = {0: torch.bfloat16, 1: torch.float16}
-NUM_CONFIGS = 8
+NUM_CONFIGS = 9
 
 
 @pytest.fixture(scope="module")
@@ -273,7 +273,8 @@ def test_binding_accepts_strided_c_view(gk):
 
 
 # ------------------------------------------- persistence / determinism / reuse
-@pytest.mark.parametrize("config,max_ctas", [(0, 2), (0, 6), (1, 2), (1, 4), (2, 1), (2, 3), (3, 5), (4, 6), (5, 4), (6, 3)])
+@pytest.mark.parametrize("config,max_ctas", [(0, 2), (0, 6), (1, 2), (1, 4), (2, 1), (2, 3), (3, 5), (4, 6), (5, 4), (6, 3),
+                                             (7, 4), (8, 2), (8, 6)])
 def test_many_tiles_per_cta(capi, config, max_ctas):
     """Few CTAs, many tiles each: the accumulator buffers alternate and are reused, the smem
     ring wraps many times; a stale accumulator or a phase slip cannot hide."""
@@ -622,6 +623,124 @@ def test_rotated_k_loop(capi, config, shape):
     At, Bt = oracle.make_ternary_inputs(M, N, 256, 98)
     Ct = run_capi(capi, At, Bt)
     assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+@pytest.mark.parametrize("config", [0, 1, 2, 8])
+@pytest.mark.parametrize("max_ctas", [0, 4])
+def test_serpentine_k_order(capi, config, max_ctas):
+    """Every other tile of a CTA loads its K blocks last to first (k_rotate = 2): all K blocks are
+    still visited exactly once per tile, ragged last K block included."""
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"k_rotate", 2)
+    capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
+    A, B = oracle.make_inputs(1024, 1536, 840, 197)             # 840 = 13 K blocks + 8 columns
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    At, Bt = oracle.make_ternary_inputs(768, 1280, 256, 198)
+    Ct = run_capi(capi, At, Bt)
+    assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+def test_tile_256x192_covers_ragged_columns(capi):
+    """The 192-column pair tile: its accumulator slots sit 256 TMEM columns apart, its B share is 96
+    rows per CTA; N = 4096 leaves a 64-column last tile, N = 1000 a ragged one.  One-hot A makes a
+    misplaced column block visible exactly."""
+    capi.gemm_sm100_set_option(b"tile_config", 8)
+    for (M, N, K) in [(512, 4096, 128), (300, 1000, 72)]:
+        ks = (torch.arange(M) * 7) % K
+        A = torch.zeros(M, K, dtype=torch.bfloat16)
+        A[torch.arange(M), ks] = 1.0
+        B = ((torch.arange(N).view(N, 1) * 3 + torch.arange(K).view(1, K)) % 251).to(torch.bfloat16)
+        C = run_capi(capi, A, B)
+        assert torch.equal(C.view(torch.int16), B[:, ks].T.contiguous().view(torch.int16))
+
+
+def test_init_is_idempotent_and_later_launches_work(capi):
+    err = ctypes.c_int(0)
+    assert capi.gemm_sm100_init(ctypes.byref(err)) == 0 and err.value == 0
+    assert capi.gemm_sm100_init(ctypes.byref(err)) == 0
+    A, B = oracle.make_inputs(256, 512, 128, 199)
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+def test_trace_buffer_is_bound_to_its_device(capi, gk):
+    """A trace buffer is only written by launches on the device that owns it; host memory is refused."""
+    host = torch.zeros(148 * 16, dtype=torch.int64)
+    assert capi.gemm_sm100_set_trace_buffer(host.data_ptr(), host.numel() * 8) == 9
+    A, B = oracle.make_inputs(512, 512, 256, 200)
+    C = torch.empty((512, 512), dtype=torch.bfloat16, device="cuda")
+    info = gk.trace_launch(A.cuda(), B.cuda(), C)
+    gk.device_status()
+    assert info["cycles"] > 0 and info["ns"] > 0
+    assert_close(C.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+def test_repeated_calls_reuse_cached_plans_and_maps(gk):
+    """Same buffers, same shape, many calls (the cached tensor maps and plan are used from the second
+    call on), then the same storage viewed as another shape: the cache key must tell them apart."""
+    buf_a = torch.zeros(512 * 512, dtype=torch.bfloat16, device="cuda")
+    buf_b = torch.zeros(1024 * 512, dtype=torch.bfloat16, device="cuda")
+    buf_c = torch.zeros(512 * 1024, dtype=torch.bfloat16, device="cuda")
+    for (M, N, K, seed) in [(512, 1024, 512, 201), (256, 512, 1024, 202), (512, 1024, 512, 203)]:
+        A, B = oracle.make_inputs(M, N, K, seed)
+        Ad, Bd, Cd = buf_a[:M * K].view(M, K), buf_b[:N * K].view(N, K), buf_c[:M * N].view(M, N)
+        Ad.copy_(A)
+        Bd.copy_(B)
+        for _ in range(3):
+            Cd.fill_(float("nan"))
+            gk.gemm_tn_test(Ad, Bd, Cd)
+        gk.device_status()
+        assert_close(Cd.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+def test_option_change_invalidates_cached_plan(capi):
+    M, N, K = 1024, 1024, 512
+    first = capi.gemm_sm100_select_config(M, N, K, 0)
+    capi.gemm_sm100_set_option(b"tile_config", 3)
+    assert capi.gemm_sm100_select_config(M, N, K, 0) == 3
+    capi.gemm_sm100_set_option(b"tile_config", -1)
+    assert capi.gemm_sm100_select_config(M, N, K, 0) == first
+
+
+def test_split_k_workspace_is_kept_per_stream(gk):
+    """The binding keeps its K-split scratch between calls, one buffer per stream: two streams
+    running cut GEMMs at the same time must not share partial tiles."""
+    M, N, K = 256, 512, 16384
+    assert gk.workspace_bytes(M, N, K, 0) > 0
+    A1, B1 = oracle.make_inputs(M, N, K, 204)
+    A2, B2 = oracle.make_inputs(M, N, K, 205)
+    ops = [(A1.cuda(), B1.cuda()), (A2.cuda(), B2.cuda())]
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in ops]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for _ in range(4):
+        for (Ad, Bd), Cd, st in zip(ops, outs, streams):
+            with torch.cuda.stream(st):
+                gk.gemm_tn_test(Ad, Bd, Cd)
+    gk.device_status()
+    assert_close(outs[0].cpu(), oracle.c_gemm_tn_f32(A1, B1), torch.bfloat16)
+    assert_close(outs[1].cpu(), oracle.c_gemm_tn_f32(A2, B2), torch.bfloat16)
+
+
+def test_fanout_with_trace_and_forced_tiles(gk, capi):
+    """The store-to-every-output kernel in both pair tiles and in its instrumented instantiation."""
+    M, N, K = 768, 1024, 320
+    A, B = oracle.make_inputs(M, N, K, 206)
+    single = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gk.gemm_tn_test(A.cuda(), B.cuda(), single)
+    for config, traced in [(0, False), (1, False), (0, True), (1, True), (-1, False)]:
+        capi.gemm_sm100_set_option(b"tile_config", config)
+        outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(5)]
+        trace = torch.zeros(gk.num_sms() * 16, dtype=torch.int64, device="cuda")
+        if traced:
+            gk.set_trace_buffer(trace)
+        try:
+            gk.gemm_tn_fanout(A.cuda(), B.cuda(), [o.data_ptr() for o in outs], N)
+            gk.device_status()
+        finally:
+            gk.set_trace_buffer(None)
+        for o in outs:
+            assert torch.equal(o.view(torch.int16), single.view(torch.int16))
+        assert bool((trace.view(-1, 16)[:, 13] > 0).any().item()) == traced
 
 
 @pytest.mark.parametrize("group_m", [1, 3, 16, 64])

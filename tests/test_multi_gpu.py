@@ -52,19 +52,25 @@ def _worker(rank, world, port, q):
             gk.gemm_tn_nsplit(Ad, Bs, C, plan=plan)
         torch.cuda.synchronize()
         report["nccl"] = torch.equal(C.view(torch.int16), single.view(torch.int16))
-        # exchange fused into the GEMM epilogue
-        try:
-            fused = gk.FusedNSplit(M, N, torch.bfloat16, torch.device("cuda", rank))
-        except Exception as exc:  # symmetric memory not available on this machine
-            report["fused"] = f"skipped: {exc!r}"[:200]
-        else:
-            fused.C.fill_(float("nan"))
+        # exchange fused into the GEMM epilogue: two alternating copies of C and one barrier per
+        # call (three calls: both copies and a re-use), then one copy and two barriers
+        for buffers, calls in ((2, 3), (1, 2)):
+            key = f"fused{buffers}"
+            try:
+                fused = gk.FusedNSplit(M, N, torch.bfloat16, torch.device("cuda", rank), buffers=buffers)
+            except Exception as exc:  # symmetric memory not available on this machine
+                report[key] = f"skipped: {exc!r}"[:200]
+                continue
+            fused.storage.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
-            for _ in range(2):
+            same = True
+            for _ in range(calls):
                 Cf = fused(Ad, Bs)
+                same = same and torch.equal(Cf.view(torch.int16), single.view(torch.int16))
             torch.cuda.synchronize()
-            report["fused"] = torch.equal(Cf.view(torch.int16), single.view(torch.int16))
+            report[key] = same
+            del fused
         gk.device_status()
         err = oracle.normalized_max_error(single.cpu(), oracle.reference_matmul_fp32(A, B))
         report["oracle"] = err <= oracle.tolerance(torch.bfloat16)
@@ -93,4 +99,5 @@ def test_nsplit_two_gpus_matches_single_gpu():
         rep = results[rank]
         assert isinstance(rep, dict), rep
         assert rep["oracle"] is True and rep["nccl"] is True, rep
-        assert rep["fused"] is True or str(rep["fused"]).startswith("skipped"), rep
+        for key in ("fused2", "fused1"):
+            assert rep[key] is True or str(rep[key]).startswith("skipped"), rep

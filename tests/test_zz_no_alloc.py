@@ -26,7 +26,8 @@ def call_static(capi, A, B, C):
     N = B.shape[0]
     err = ctypes.c_int(0)
     stream = torch.cuda.current_stream().cuda_stream
-    rc = capi.gemm_sm100_tn_static_scratch(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0,
+    code = {torch.bfloat16: 0, torch.float16: 1}[A.dtype]
+    rc = capi.gemm_sm100_tn_static_scratch(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, K, K, N, code,
                                            stream, ctypes.byref(err))
     return rc, err.value
 
@@ -65,6 +66,30 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(capi):
         assert torch.equal(got.view(torch.int16), C_same.cpu().view(torch.int16))
         assert oracle.normalized_max_error(got, C_auto.cpu().float()) <= oracle.tolerance(torch.bfloat16)
         assert oracle.normalized_max_error(got, oracle.reference_matmul_fp32(A, B)) <= oracle.tolerance(torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_static_scratch_same_problem_twice_and_fp16(capi, dtype):
+    """The same problem twice in a row on the shared array (the second call finds the first call's
+    counters and partial tiles in it and must not be fooled by them), in both element types:
+    both results equal, bit for bit, the workspace entry point forced onto the same schedule."""
+    reset(capi)
+    M, N, K = 24, 3000 + 8, 4096 + 64
+    A, B = oracle.make_inputs(M, N, K, 92, dtype, a_std=1.0, b_std=0.02)
+    Ad, Bd = A.cuda(), B.cuda()
+    capi.gemm_sm100_set_option(b"tile_config", 2)
+    capi.gemm_sm100_set_option(b"split_k", 1)
+    C_same = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+    assert capi_gemm(capi, Ad, Bd, C_same) == 0
+    reset(capi)
+    assert capi_status(capi) == (0, 0)
+    want = C_same.cpu()
+    assert oracle.normalized_max_error(want, oracle.reference_matmul_fp32(A, B)) <= oracle.tolerance(dtype)
+    for _ in range(2):
+        C_static = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+        assert call_static(capi, Ad, Bd, C_static) == (0, 0)
+        assert capi_status(capi) == (0, 0)
+        assert torch.equal(C_static.cpu().view(torch.int16), want.view(torch.int16))
 
 
 def test_static_scratch_refuses_what_does_not_fit(capi):
