@@ -8,6 +8,20 @@ and 30 timed iterations each; the speed-up is the median of the per-iteration ra
 created once per shape, L2 flushed between iterations by writing a 512 MiB scratch buffer (the reference allocates an 80 MB tensor per run,
 :58-61), a B200 entry in the peak table (:592-599 has none), and one JSON line per shape.
 Its ctypes-cuBLAS autotuner (:124-276) is not reproduced.
+
+A/B mode (the tables under profiles/ that compare tile configurations and K-split schedules come
+from it): `--ab` takes variants as `name:option=value,option=value;...` (options of
+gemm_kernels.set_option; `auto` = the library's own choice, `mm` = torch.mm), `--shapes` a list of
+MxNxK.  The variants are timed in alternation in one process, `--rounds` rounds of `--iters`
+back-to-back launches each (or, with `--flush`, single launches with an L2 flush before each),
+CUDA events; the table gives the median time per launch and the median per-round ratio to the first
+variant.  Under the power cap the clock drifts within seconds, so only numbers from one run of this
+mode are comparable.
+
+    python cute-examples_b200/tests/gemm_bench.py --shapes 4096x4096x4096,8192x8192x8192 \
+        --ab "c0:tile_config=0;c1:tile_config=1;c8:tile_config=8;auto;mm" --flush
+    python cute-examples_b200/tests/gemm_bench.py --ksplit-table
+    python cute-examples_b200/tests/gemm_bench.py --fanout 1,4,8 --shapes 8192x4096x8192
 """
 import argparse
 import json
@@ -90,13 +104,134 @@ def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     return rec
 
 
+OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": 0, "max_ctas": 0}
+
+KSPLIT_SHAPES = ("512x4096x4096,1024x4096x4096,256x8192x8192,256x512x65536,512x512x32768,1024x1024x16384,"
+                 "2048x2048x8192,1024x2048x8192,512x4096x8192,128x2048x16384,256x256x32768,1024x1024x4096,"
+                 "2048x1024x4096,512x1024x65536")
+KSPLIT_VARIANTS = ("c0:tile_config=0,split_k=0;c3:tile_config=3,split_k=0;c2s:tile_config=2,split_k=1;"
+                   "c0e2:tile_config=0,split_k=2;c0e4:tile_config=0,split_k=4;c0e8:tile_config=0,split_k=8;"
+                   "c2e2:tile_config=2,split_k=2;c2e4:tile_config=2,split_k=4;c2e8:tile_config=2,split_k=8;auto;mm")
+
+
+def parse_variants(text):
+    out = []
+    for item in text.split(";"):
+        item = item.strip()
+        if not item:
+            continue
+        name, _, opts = item.partition(":")
+        settings = {}
+        for kv in opts.split(","):
+            if kv.strip():
+                k, v = kv.split("=")
+                settings[k.strip()] = int(v)
+        out.append((name.strip(), settings))
+    return out
+
+
+def apply_options(settings):
+    for k, v in OPTION_DEFAULTS.items():
+        gk.set_option(k, settings.get(k, v))
+
+
+def timed(fn, iters, scratch=None):
+    """µs per call: `iters` back-to-back calls between two events, or (with a scratch buffer)
+    single calls with an L2 flush before each, median."""
+    if scratch is None:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        e.synchronize()
+        return s.elapsed_time(e) / iters * 1e3
+    times = []
+    for _ in range(iters):
+        scratch.add_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        times.append(s.elapsed_time(e) * 1e3)
+    return statistics.median(times)
+
+
+def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None):
+    """Interleaved timing of option variants (and torch.mm) per shape; one JSON line per shape."""
+    for (M, N, K) in shapes:
+        A = (torch.randn((M, K), device="cuda") / K ** 0.5).to(dtype)
+        B = (torch.randn((N, K), device="cuda") / K ** 0.5).to(dtype)
+        C = torch.empty((M, N), device="cuda", dtype=dtype)
+        n_iters = iters if iters > 0 else max(5, min(50, int(20e-3 / (2.0 * M * N * K / 1.4e15 + 8e-6))))
+        calls = {}
+        outs = None
+        if fanout:
+            outs = [torch.empty((M, N), device="cuda", dtype=dtype) for _ in range(max(fanout))]
+        for name, settings in variants:
+            if name == "mm":
+                calls[name] = (settings, lambda: torch.mm(A, B.T, out=C))
+            elif fanout:
+                for n_out in fanout:
+                    ptrs = [o.data_ptr() for o in outs[:n_out]]
+                    calls[f"{name}/out{n_out}"] = (settings, lambda ptrs=ptrs: gk.gemm_tn_fanout(A, B, ptrs, N))
+            else:
+                calls[name] = (settings, lambda: gk.gemm_tn_test(A, B, C))
+        res = {k: [] for k in calls}
+        for k, (settings, fn) in calls.items():
+            apply_options(settings)
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        for _ in range(rounds):
+            for k, (settings, fn) in calls.items():
+                apply_options(settings)
+                res[k].append(timed(fn, n_iters, scratch))
+        apply_options({})
+        gk.device_status()
+        first = next(iter(res))
+        rec = {"M": M, "N": N, "K": K, "dtype": str(dtype).replace("torch.", ""), "rounds": rounds, "iters": n_iters,
+               "flush": scratch is not None,
+               "auto": gk.describe_config(gk.select_config(M, N, K, gk.DTYPE_CODES[dtype])),
+               "auto_workspace_bytes": gk.workspace_bytes(M, N, K, gk.DTYPE_CODES[dtype]),
+               "us": {k: round(statistics.median(v), 2) for k, v in res.items()},
+               "ratio_to_first": {k: round(statistics.median(a / b for a, b in zip(v, res[first])), 4)
+                                  for k, v in res.items()},
+               "tflops": {k: round(2.0 * M * N * K / statistics.median(v) / 1e6, 1) for k, v in res.items()},
+               "gbs": {k: round(2.0 * (M * K + N * K + M * N) / statistics.median(v) / 1e3, 1) for k, v in res.items()}}
+        print(f"{M}x{N}x{K}: " + "  ".join(f"{k} {rec['us'][k]:.1f}us (x{rec['ratio_to_first'][k]:.3f})" for k in res),
+              flush=True)
+        print(json.dumps(rec), flush=True)
+        del A, B, C, outs
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--quick", action="store_true", help="skip the largest shapes")
     ap.add_argument("--layout", default="tn", choices=["tn", "nn"], help="B as [N,K] (tn) or as [K,N] (nn)")
+    ap.add_argument("--ab", default=None, help="A/B mode: variants 'name:opt=val,...;name2:...;auto;mm'")
+    ap.add_argument("--shapes", default=None, help="A/B mode: comma-separated MxNxK")
+    ap.add_argument("--rounds", type=int, default=6)
+    ap.add_argument("--iters", type=int, default=0, help="launches per round (0 = about 20 ms worth)")
+    ap.add_argument("--flush", action="store_true", help="A/B mode: single launches with an L2 flush before each")
+    ap.add_argument("--ksplit-table", action="store_true", help="A/B mode preset: K-split schedules on few-tile problems")
+    ap.add_argument("--fanout", default=None, help="A/B mode on gemm_tn_fanout with these output counts (local buffers)")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    if args.ksplit_table:
+        args.ab = args.ab or KSPLIT_VARIANTS
+        args.shapes = args.shapes or KSPLIT_SHAPES
+        args.iters = args.iters or 50
+    if args.ab or args.fanout:
+        shapes = [tuple(int(x) for x in sh.split("x")) for sh in (args.shapes or "8192x8192x8192").split(",")]
+        variants = parse_variants(args.ab or "auto")
+        scratch = torch.zeros(512 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda") if args.flush else None
+        fanout = [int(x) for x in args.fanout.split(",")] if args.fanout else None
+        print(f"device: {torch.cuda.get_device_name()}  SMs: {gk.num_sms()}")
+        ab_table(shapes, variants, dtype, args.rounds, args.iters, scratch, fanout)
+        return
     name, peak = peak_for_device()
     print(f"device: {torch.cuda.get_device_name()}  SMs: {gk.num_sms()}  nominal dense peak: {peak} TFLOP/s ({name})")
     scratch = torch.zeros(512 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda")

@@ -1,7 +1,8 @@
 """Profiling target: a few launches of gemm_tn_test on one shape, nothing else.
 
 Successor of the reference's kernels/tests/profiler.py:1-12 (one 4096 x 4096 launch meant to be
-run under Nsight).  Run it under `ncu --clock-control none -k regex:gemm_tn ...`.
+run under Nsight).  tests/ncu_capture.py runs it under `ncu --clock-control none -k regex:gemm_tn ...`
+and prints the counter table.
 """
 import argparse
 import os
@@ -20,11 +21,15 @@ ap.add_argument("--k", type=int, default=4096)
 ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
 ap.add_argument("--launches", type=int, default=3)
 ap.add_argument("--tile-config", type=int, default=-1)
+ap.add_argument("--option", action="append", default=[], help="name=value for gemm_kernels.set_option")
 args = ap.parse_args()
 
 dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
 device = "cuda"
 set_option("tile_config", args.tile_config)
+for item in args.option:
+    name, value = item.split("=")
+    set_option(name, int(value))
 A = (torch.randn((args.m, args.k), device=device) / args.k ** 0.5).to(dtype)
 B = (torch.randn((args.n, args.k), device=device) / args.k ** 0.5).to(dtype)
 C_custom = torch.empty((args.m, args.n), device=device, dtype=dtype)
