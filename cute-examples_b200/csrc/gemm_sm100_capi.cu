@@ -73,7 +73,9 @@ std::atomic<long> g_opt_timeout_ms{2000};
 std::atomic<long> g_opt_max_ctas{0};
 std::atomic<long> g_opt_debug_flags{0};
 std::atomic<long> g_opt_group_m{0};
-std::atomic<long> g_opt_k_rotate{0};    // 0 never (default: measured no gain on B200), 1 always, -1 when there is a single tile row
+std::atomic<long> g_opt_k_rotate{-1};   // 0 never, 1 always, -1 (default) when there is a single tile row: 3 % on the few-row shapes, 2 = serpentine
+std::atomic<long> g_opt_tiles_n{0};    // > 0: force this many tiles per tile row (tests), when the configuration allows the widths
+std::atomic<long> g_opt_balance{1};    // 1: the planner may choose a balanced column tiling; 0: uniform tiles only
 std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
 // Bumped by every gemm_sm100_set_option: cached plans of an older generation are stale.
 std::atomic<unsigned> g_opt_generation{1};
@@ -267,7 +269,7 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // The 256 x 128 pair tile (7) only matters when a problem has too few tiles for anything wider:
 // it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).
 constexpr double kConfigRate[kNumConfigs] = {0.99, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545, 0.955};
-constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 1.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
 // in K blocks of that tile.
 constexpr double kFanoutKBlocksPerOutput = 12.0;
@@ -278,6 +280,9 @@ constexpr bool has_split_k(int config) { return config == 0 || config == 1 || co
 constexpr bool has_even_split(int config) { return config == 0 || config == 2; }
 // Configurations with a store-to-every-output kernel (the pair tiles of the multi-GPU path).
 constexpr bool has_fanout(int config) { return config == 0 || config == 1; }
+// Configurations the planner may give a balanced column tiling (256-column MMAs; the others are
+// special-purpose small tiles).
+constexpr bool has_balanced(int config) { return config == 0 || config == 1 || config == 2; }
 // Configurations with kernels for the other operand layouts and alpha / beta.
 constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // Even split: what cutting costs per wave of units on top of the K blocks, in K blocks of the
@@ -288,6 +293,8 @@ constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.
 
 struct Plan {
   int config = 0;
+  // Column tiling (TileParams::bal_q / bal_rem): tiles_n tiles per tile row; 0 = uniform tiles.
+  int tiles_n = 0, bal_q = 0, bal_rem = 0;
   bool split_k = false;
   int ctas = 0;              // grid size
   size_t flag_bytes = 0;     // K-split: arrival counters (one per CTA), padded to 256 bytes
@@ -303,9 +310,57 @@ inline int grid_cap(const ConfigInfo& c, int sm_count) {
   return static_cast<int>(cap);
 }
 
+// Host mirror of the kernel's tile_coords(): column-tile index of tile `t`.
+inline int n_tile_of(long t, int m_tiles, int n_tiles, int group_m) {
+  const long per_group = static_cast<long>(group_m) * n_tiles;
+  const long group = t / per_group;
+  const long in_group = t - group * per_group;
+  const long first_m = group * group_m;
+  const long rows = (m_tiles - first_m) < group_m ? (m_tiles - first_m) : group_m;
+  return static_cast<int>(in_group / rows);
+}
+
+inline int default_group_m(int m_tiles) {
+  return g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (m_tiles >= 16 ? 16 : 8);
+}
+
+// What one K block of a tile of `width` columns costs, in columns of a full-rate tile: the MMAs
+// take time in proportion to the width, the operand loads (A tile + this CTA's share of B) in
+// proportion to their bytes, and the SM gets about 63 bytes per clock from L2 when every SM is
+// pulling (trace counters with the MMAs switched off: the 256 x 256 pair tile loads 1.04x as fast
+// as it computes, the 256 x 192 tile only 0.80x).  Normalised so that the configuration's full
+// tile costs its own width (its measured rate is in kConfigRate).
+double effective_width(const ConfigInfo& c, int width) {
+  const int full = c.mma_n * c.halves;
+  auto cycles = [&](int w) {
+    const double mma = 2.0 * w;                                              // 4 MMAs of w / 2 cycles
+    const double load = (128.0 * 64 * 2 + static_cast<double>(w) / c.cta_group * 64 * 2) / 63.0;
+    return mma > load ? mma : load;
+  };
+  return cycles(width) / cycles(full) * full;
+}
+
+// Longest chain of work any CTA (pair) gets under the static persistent schedule, for `tiles_n`
+// tiles per tile row dealt as the kernel deals them; in effective columns.
+double schedule_cost(const ConfigInfo& c, int m_tiles, int tiles_n, int q, int rem, long slots) {
+  const long tiles = static_cast<long>(m_tiles) * tiles_n;
+  const long clusters = tiles < slots ? tiles : slots;
+  const int group_m = default_group_m(m_tiles);
+  const double wide = effective_width(c, (q + 1) * 64), narrow = effective_width(c, q * 64);
+  double worst = 0.0;
+  for (long cl = 0; cl < clusters; ++cl) {
+    double sum = 0.0;
+    for (long t = cl; t < tiles; t += clusters)
+      sum += n_tile_of(t, m_tiles, tiles_n, group_m) < rem ? wide : narrow;
+    if (sum > worst) worst = sum;
+  }
+  return worst;
+}
+
 // The K-split schedule gives every CTA the same number of K blocks; it pays when whole tiles
 // quantise badly over the SMs (few tiles, as in the memory-bound small-M shapes) and K is long.
-Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int config_limit = kNumConfigs) {
+Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int config_limit = kNumConfigs,
+               bool allow_balance = true) {
   Plan best;
   double best_cost = 1e300;
   const long k_blocks = ceil_div(K, 64);
@@ -327,6 +382,51 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     // costs in units of (one K block of one tile column) per CTA
     const double boundary = kTileBoundaryKBlocks[i];
     double cost = static_cast<double>(waves) * block_n * (k_blocks + boundary) / rate;
+    // Balanced column tiling (whole tiles only): another number of tiles per tile row, the
+    // chunks of 64 columns dealt evenly, when the static schedule's longest chain gets shorter
+    // by more than 2 %.  Skipped for problems of many waves, where quantisation costs little.
+    if (allow_balance && g_opt_balance.load() != 0 && has_balanced(i) && (waves <= 24 || g_opt_tiles_n.load() > 0) && N >= 64) {
+      const int m_tiles = static_cast<int>(ceil_div(M, 128L * c.cta_group));
+      const int chunks = static_cast<int>(ceil_div(N, 64));
+      const int q_full = block_n / 64;
+      // double-width tiles keep both halves busy; single-width tiles narrower than 192 columns load
+      // more operand bytes per flop than the ring delivers (and few-tile problems are better off
+      // with the small-tile configurations and their deeper rings)
+      const int q_min = c.halves == 2 ? c.mma_n / 64 + 1 : 3;
+      const int t_uniform = static_cast<int>(ceil_div(chunks, q_full));
+      int t_last = chunks / q_min;
+      if (t_last > 2 * t_uniform + 2) t_last = 2 * t_uniform + 2;
+      double best_chain = static_cast<double>(waves) * block_n;
+      // A single tile row (the memory-bound few-row shapes): ties go to more tiles, because every
+      // tile is one more SM that streams its share of B.
+      const bool single_row = m_tiles == 1;
+      const int forced_t = static_cast<int>(g_opt_tiles_n.load());
+      for (int t_n = single_row ? t_uniform + 1 : t_uniform; t_n <= t_last || forced_t > 0; ++t_n) {
+        if (forced_t > 0) t_n = forced_t;
+        const int q = chunks / t_n, rem = chunks % t_n;
+        if (forced_t > 0) {
+          if (t_n <= chunks && q >= q_min && q + (rem ? 1 : 0) <= q_full) {
+            best_chain = schedule_cost(c, m_tiles, t_n, q, rem, slots);
+            cand.tiles_n = t_n, cand.bal_q = q, cand.bal_rem = rem;
+          }
+          break;
+        }
+        if (q < q_min || q + (rem ? 1 : 0) > q_full) continue;
+        if (static_cast<long>(m_tiles) * t_n > 40000) break;
+        const double chain = schedule_cost(c, m_tiles, t_n, q, rem, slots);
+        if (chain < best_chain * 0.98) {
+          best_chain = chain;
+          cand.tiles_n = t_n;
+          cand.bal_q = q;
+          cand.bal_rem = rem;
+        }
+      }
+      if (cand.tiles_n > 0) {
+        const long bal_tiles = static_cast<long>(m_tiles) * cand.tiles_n;
+        cand.ctas = static_cast<int>((bal_tiles < slots ? bal_tiles : slots) * c.cta_group);
+        cost = best_chain * (k_blocks + boundary) / rate;
+      }
+    }
     const long units = tiles * k_blocks;
     // K-split.  Forced (split_k = 1): as many ranges as CTA (pair)s.  Automatic: the 128 x 256
     // tile only, when whole tiles would leave more than half of the SMs idle, with the number of
@@ -380,6 +480,7 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     if (even_s > 0 && (g_opt_split_k > 1 || even_cost < best_other)) {
       const long even_units = tiles * even_s;
       cost = even_cost * 1.1;                                // ties go to the simpler schedule
+      cand.tiles_n = cand.bal_q = cand.bal_rem = 0;          // cut tiles are uniform
       cand.split_k = true;
       cand.split_factor = even_s;
       cand.ctas = static_cast<int>((even_units < slots ? even_units : slots) * c.cta_group);
@@ -388,6 +489,7 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
       cand.partial_bytes = static_cast<size_t>(even_units) * c.cta_group * cand.partial_rows * block_n * sizeof(float);
     } else if (can_split && (g_opt_split_k == 1 || auto_split)) {
       cost = split_cost;
+      cand.tiles_n = cand.bal_q = cand.bal_rem = 0;
       cand.split_k = true;
       cand.ctas = static_cast<int>(ranges * c.cta_group);
       cand.partial_rows = M < 128 ? static_cast<int>((M + 31) / 32 * 32) : 128;
@@ -404,10 +506,11 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
 
 // Per-thread cache of plans: the binding asks for the workspace size and then launches, and callers
 // repeat shapes, so the cost model runs once per (shape, option state).
-Plan plan_for(int M, int N, int K, int sm_count, bool allow_split = true, int config_limit = kNumConfigs) {
+Plan plan_for(int M, int N, int K, int sm_count, bool allow_split = true, int config_limit = kNumConfigs,
+              bool allow_balance = true) {
   struct Entry {
     int M = -1, N = 0, K = 0, sm = 0, limit = 0;
-    bool allow = false;
+    bool allow = false, balance = false;
     unsigned generation = 0;
     Plan plan;
   };
@@ -418,13 +521,14 @@ Plan plan_for(int M, int N, int K, int sm_count, bool allow_split = true, int co
   for (int i = 0; i < kEntries; ++i) {
     const Entry& e = cache[i];
     if (e.M == M && e.N == N && e.K == K && e.sm == sm_count && e.limit == config_limit && e.allow == allow_split &&
-        e.generation == generation)
+        e.balance == allow_balance && e.generation == generation)
       return e.plan;
   }
   Entry& e = cache[next++ % kEntries];
   e.M = M, e.N = N, e.K = K, e.sm = sm_count, e.limit = config_limit, e.allow = allow_split;
+  e.balance = allow_balance;
   e.generation = generation;
-  e.plan = make_plan(M, N, K, sm_count, allow_split, config_limit);
+  e.plan = make_plan(M, N, K, sm_count, allow_split, config_limit, allow_balance);
   return e.plan;
 }
 
@@ -441,7 +545,10 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.k_blocks = static_cast<int>(ceil_div(p.K, Cfg::kBlockK));
   // Rasterisation group: 16 tile rows when the problem has that many (measured best from 8192
   // to 32768 rows: the A panel of a group is reused by more B tiles), else 8.
-  tp.group_m = g_opt_group_m.load() > 0 ? static_cast<int>(g_opt_group_m.load()) : (tp.m_tiles >= 16 ? 16 : 8);
+  tp.group_m = default_group_m(tp.m_tiles);
+  tp.bal_q = Cfg::kBlockN / 64;
+  tp.bal_rem = 0;
+  tp.b_box_rows = Cfg::kBRows;
   tp.status = st.status_ptr;
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
   tp.trace = nullptr;
@@ -554,9 +661,21 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   cudaError_t e;
 
   TileParams tp = base_tile_params<Cfg>(p, st);
+  int b_box = Cfg::kBRows;
+  if (plan.tiles_n > 0) {
+    tp.n_tiles = plan.tiles_n;
+    tp.bal_q = plan.bal_q;
+    tp.bal_rem = plan.bal_rem;
+    b_box = 64 / Cfg::kCtaGroup;          // tile widths are multiples of 64 columns: this CTA's share of them
+    tp.b_box_rows = b_box;
+  }
   tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
   const long k_order = g_opt_k_rotate.load();
-  tp.k_rotate = k_order == 2 ? 2 : ((k_order == 1 || (k_order < 0 && tp.m_tiles == 1 && !plan.split_k)) ? 1 : 0);
+  // Automatic (-1): only the memory-bound few-row regime (at most 128 rows, thousands of columns).
+  // Other problems keep K ascending, so that the same rows give the same bits whether they are
+  // computed in one call or in row panels.
+  const bool few_rows = p.M <= 128 && p.N >= 2048 && !plan.split_k;
+  tp.k_rotate = k_order == 2 ? 2 : ((k_order == 1 || (k_order < 0 && few_rows)) ? 1 : 0);
   if (plan.split_k) {
     tp.sk_flags = static_cast<unsigned int*>(workspace);
     tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
@@ -569,7 +688,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   CUtensorMap map_a, map_b, map_c;
   rc = encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
   if (rc) return rc;
-  rc = encode_2d_cached(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, Cfg::kBRows, cuda_error_out);
+  rc = encode_2d_cached(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, b_box, cuda_error_out);
   if (rc) return rc;
   rc = encode_2d_cached(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
   if (rc) return rc;
@@ -863,7 +982,7 @@ int gemm_sm100_gemm_scaled(const void* A, const void* B, void* C, int M, int N, 
     rc = get_encoder(cuda_error_out);
     if (rc != GEMM_SM100_OK) return rc;
   }
-  Plan plan = plan_for(M, N, K, st->sm_count, /*allow_split=*/false, /*config_limit=*/4);
+  Plan plan = plan_for(M, N, K, st->sm_count, /*allow_split=*/false, /*config_limit=*/4, /*allow_balance=*/false);
   if (plan.config > 3) plan = Plan{};       // (a forced configuration without such a variant)
   if (plan.ctas == 0) {
     const long tiles = ceil_div(M, 256L) * ceil_div(N, 256L);
@@ -957,6 +1076,16 @@ int gemm_sm100_set_option(const char* name, long value) {
     g_opt_split_k = value;
     return GEMM_SM100_OK;
   }
+  if (std::strcmp(name, "tiles_n") == 0) {
+    if (value < 0 || value > (1 << 20)) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_tiles_n = value;
+    return GEMM_SM100_OK;
+  }
+  if (std::strcmp(name, "balance") == 0) {
+    if (value < 0 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_balance = value;
+    return GEMM_SM100_OK;
+  }
   if (std::strcmp(name, "group_m") == 0) {
     if (value < 0 || value > 4096) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_group_m = value;
@@ -997,6 +1126,31 @@ int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes) {
   const int tmem_cols = 2 * c.mma_n <= 128 ? 128 : (2 * c.mma_n <= 256 ? 256 : 512);
   std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d epilogue_warps=%d",
                 c.cta_group, 128 * c.cta_group, c.mma_n * c.halves, c.stages, tmem_cols, c.epi_warps);
+  return GEMM_SM100_OK;
+}
+
+int gemm_sm100_describe_plan(int M, int N, int K, int dtype, char* buf, size_t buf_bytes) {
+  (void)dtype;
+  if (!buf || buf_bytes == 0) return GEMM_SM100_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0) return GEMM_SM100_ERR_BAD_SHAPE;
+  const Plan plan = plan_for(M, N, K, current_sm_count());
+  const ConfigInfo& c = kConfigs[plan.config];
+  const int block_n = c.mma_n * c.halves;
+  char tiling[96];
+  if (plan.tiles_n > 0)
+    std::snprintf(tiling, sizeof(tiling), "balanced: %d tiles per row, %d x %d + %d x %d columns", plan.tiles_n,
+                  plan.bal_rem, (plan.bal_q + 1) * 64, plan.tiles_n - plan.bal_rem, plan.bal_q * 64);
+  else
+    std::snprintf(tiling, sizeof(tiling), "uniform: %ld tiles per row of %d columns", ceil_div(N, block_n), block_n);
+  char split[64];
+  if (!plan.split_k)
+    std::snprintf(split, sizeof(split), "whole tiles");
+  else if (plan.split_factor > 1)
+    std::snprintf(split, sizeof(split), "every tile cut into %d K ranges", plan.split_factor);
+  else
+    std::snprintf(split, sizeof(split), "contiguous K ranges");
+  std::snprintf(buf, buf_bytes, "config=%d tile=%dx%dx64 %s; %s; ctas=%d workspace=%zu", plan.config, 128 * c.cta_group,
+                block_n, tiling, split, plan.ctas, plan.split_k ? plan.flag_bytes + plan.partial_bytes : size_t{0});
   return GEMM_SM100_OK;
 }
 

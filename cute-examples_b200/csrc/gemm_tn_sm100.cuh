@@ -59,6 +59,15 @@ struct TileParams {
   int n_tiles;   // ceil(N / kBlockN)
   int k_blocks;  // ceil(K / 64)
   int group_m;   // tiles along M per rasterisation group
+  // Column tiling.  The N / 64 chunks of 64 columns are dealt to the n_tiles tiles of a tile row:
+  // tile j covers (bal_q + (j < bal_rem)) chunks, starting at chunk j * bal_q + min(j, bal_rem).
+  // Uniform tiles of kBlockN columns are bal_q = kBlockN / 64, bal_rem = 0 (the last tile hangs
+  // over the edge: loads are zero-filled, stores clipped).  A balanced tiling gives the tile row
+  // the number of tiles that fills the SMs evenly and makes the tiles as wide as that allows,
+  // e.g. 4096 columns as 8 x 448 + 1 x 512 instead of 8 x 512.  Widths are at most kBlockN and,
+  // for double-width configurations, more than kMmaN (both halves non-empty).
+  int bal_q, bal_rem;
+  int b_box_rows;  // rows per TMA box of B: kBRows for uniform tiles, 64 / kCtaGroup for balanced ones
   unsigned int* status;            // device word, 0 = ok
   unsigned long long timeout_ns;   // bound of every device-side wait
   unsigned long long* trace;       // optional: kTraceWords counters per CTA (nullptr = off)
@@ -302,6 +311,22 @@ __device__ __forceinline__ void tile_coords(int tile, const TileParams& p, int& 
   n_tile = in_group / rows;
 }
 
+// Columns of tile `n_tile` of a tile row: first column, width of the first accumulator half and of
+// the second one (0 for single-width configurations).
+struct TileCols {
+  int col0, w0, w1;
+};
+template <class Cfg>
+__device__ __forceinline__ TileCols tile_columns(int n_tile, const TileParams& p) {
+  const bool wide = n_tile < p.bal_rem;
+  const int width = (p.bal_q + (wide ? 1 : 0)) * Cfg::kEpiCols;
+  TileCols t;
+  t.col0 = (n_tile * p.bal_q + (wide ? n_tile : p.bal_rem)) * Cfg::kEpiCols;
+  t.w0 = (Cfg::kHalves == 1 || width < Cfg::kMmaN) ? width : Cfg::kMmaN;
+  t.w1 = width - t.w0;
+  return t;
+}
+
 template <bool kIsBf16>
 __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
   const float lo = __uint_as_float(lo_bits), hi = __uint_as_float(hi_bits);
@@ -437,7 +462,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
       Segment seg;
       bool have = work.next(seg);
-      int kb = seg.kb0, row_a = 0, row_b = 0, rot = 0, tiles_done = 0;
+      int kb = seg.kb0, row_a = 0, rot = 0, tiles_done = 0;
+      int row_b[2] = {0, 0}, rows_b[2] = {0, 0};          // this CTA's first row and row count of B per half
+      uint32_t tx_bytes = 0;
+      const int b_box = p.b_box_rows;
       bool seg_start = true, backwards = false;
       bool ok = true;
       long long stall = 0;
@@ -449,7 +477,12 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             int m_tile, n_tile;
             tile_coords(seg.tile, p, m_tile, n_tile);
             row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
-            row_b = n_tile * Cfg::kBlockN + (int)cta_rank * Cfg::kBRows;
+            const TileCols tc = tile_columns<Cfg>(n_tile, p);
+            rows_b[0] = tc.w0 / G;
+            rows_b[1] = tc.w1 / G;
+            row_b[0] = tc.col0 + (int)cta_rank * rows_b[0];
+            row_b[1] = tc.col0 + tc.w0 + (int)cta_rank * rows_b[1];
+            tx_bytes = (uint32_t)(Cfg::kABytes + (rows_b[0] + rows_b[1]) * Cfg::kBlockK * 2) * G;
             rot = p.k_rotate == 1 ? (int)(((long long)seg.tile * k_blocks) / num_tiles) : 0;
             backwards = !kSplitK && p.k_rotate == 2 && (tiles_done & 1);
             ++tiles_done;
@@ -468,7 +501,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           if (backwards) kb_phys = k_blocks - 1 - kb;
           const int x = kb_phys * Cfg::kBlockK;
           if (issuer) {
-            if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, Cfg::kStageBytes * G);
+            if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, tx_bytes);
             if constexpr (!kAIsKM) {
               tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
             } else {
@@ -481,14 +514,18 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
 #pragma unroll
             for (int h = 0; h < Cfg::kHalves; ++h) {
               if constexpr (!kBIsKN) {
-                tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, x,
-                               row_b + h * Cfg::kMmaN, pol);
+                // one box of b_box rows at a time (a single box for uniform tiles)
+#pragma unroll 1
+                for (int j = 0; j < rows_b[h]; j += b_box)
+                  tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes + j * (Cfg::kBlockK * 2), &tmap_b,
+                                 full_leader + 8u * s, x, row_b[h] + j, pol);
               } else {
-                // B[K, N]: coordinates are (column of B, K); one 64 x 64 box per block of 64 columns
+                // B[K, N] (uniform tiles only): coordinates are (column of B, K); one 64 x 64 box per
+                // block of 64 columns
 #pragma unroll
                 for (int j = 0; j < Cfg::kBRows / 64; ++j)
                   tma_load_2d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes + j * 8192, &tmap_b,
-                                 full_leader + 8u * s, row_b + h * Cfg::kMmaN + j * 64, x, pol);
+                                 full_leader + 8u * s, row_b[h] + j * 64, x, pol);
               }
             }
           }
@@ -516,8 +553,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       const bool issuer = elect_one();
       bool peer_ready = true;
       if constexpr (G == 2) peer_ready = wait_bounded(bar_base + kTmemReadyOff, 0u, ctx, kStatusTimeoutMmaAcc + 0xf);
-      constexpr uint32_t idesc =
-          make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, Cfg::kMmaN, kBIsKN ? 1u : 0u, kAIsKM ? 1u : 0u);
+      // instruction descriptor without N: the width of each half is a property of the tile
+      constexpr uint32_t idesc_base =
+          make_idesc_f16(Cfg::kIsBf16 ? 1u : 0u, Cfg::kBlockM * G, 0, kBIsKN ? 1u : 0u, kAIsKM ? 1u : 0u);
+      uint32_t idesc_h[2] = {idesc_base, idesc_base};
       const uint64_t da0 = kAIsKM ? make_smem_desc_sw128_mn(smem_a, 8192) : make_smem_desc_sw128(smem_a);
       constexpr uint32_t kAStepK = kAIsKM ? 128u : 2u;
       const uint64_t db0 = kBIsKN ? make_smem_desc_sw128_mn(smem_b, 8192) : make_smem_desc_sw128(smem_b);
@@ -556,6 +595,13 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           tc_fence_after_sync();
           const bool first_kb = kb == seg.kb0;
           const bool last_kb = kb == seg.kb1 - 1;
+          if (first_kb) {
+            int m_tile, n_tile;
+            tile_coords(seg.tile, p, m_tile, n_tile);
+            const TileCols tc = tile_columns<Cfg>(n_tile, p);
+            idesc_h[0] = idesc_base | ((uint32_t)(tc.w0 >> 3) << 17);
+            idesc_h[1] = idesc_base | ((uint32_t)(tc.w1 >> 3) << 17);
+          }
 #pragma unroll
           for (int h = 0; h < Cfg::kHalves; ++h) {
             // accumulator slot of this half, and the parity of its hand-over barriers
@@ -580,10 +626,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             const uint64_t db = db0 + (uint64_t)((s * Cfg::kBBytes + h * Cfg::kBHalfBytes) >> 4);
             if (issuer) {
               if (!skip_mma) {
-                umma_f16<G>(tmem_d, da, db, idesc, first_kb ? 0u : 1u);   // first K step of a segment overwrites
+                umma_f16<G>(tmem_d, da, db, idesc_h[h], first_kb ? 0u : 1u);   // first K step of a segment overwrites
 #pragma unroll
                 for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k)
-                  umma_f16<G>(tmem_d, da + kAStepK * k, db + kBStepK * k, idesc, 1u);
+                  umma_f16<G>(tmem_d, da + kAStepK * k, db + kBStepK * k, idesc_h[h], 1u);
               }
               if (last_kb) {                                             // this half's accumulator is complete
                 if (skip_mma) {
@@ -647,6 +693,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       int m_tile, n_tile;
       tile_coords(seg.tile, p, m_tile, n_tile);
       const int row0 = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + q * 32;
+      const TileCols tcols = tile_columns<Cfg>(n_tile, p);
       const bool row_live = row0 + (int)lane < p.M;          // rows past M hold zeros: never moved
       // Contiguous ranges: a segment that does not start its tile leaves a partial tile for the
       // tile's owner.  Even split: every contributor leaves one, nobody owns the tile.
@@ -675,7 +722,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       for (int h = 0; ok && h < Cfg::kHalves; ++h) {
         const int slot = Cfg::kHalves == 1 ? (iter & 1) : h;
         const uint32_t slot_phase = Cfg::kHalves == 1 ? ((iter >> 1) & 1u) : (iter & 1u);
-        const int col0 = n_tile * Cfg::kBlockN + h * Cfg::kMmaN;
+        const int col0 = tcols.col0 + (h ? tcols.w0 : 0);
+        const int chunks_h = (h ? tcols.w1 : tcols.w0) / Cfg::kEpiCols;    // 64-column chunks of this half
         long long te = 0;
         if constexpr (kDebug) te = trace ? clock64() : 0;
         if (!wait_bounded(bar_base + kTFullOff + 8u * slot, slot_phase, ctx, kStatusTimeoutEpilogue + slot)) {
@@ -766,7 +814,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               }
             }
           }
-          const bool live = (row0 < p.M) && (col0 + c * Cfg::kEpiCols < p.N) &&
+          const bool live = (row0 < p.M) && (c < chunks_h) && (col0 + c * Cfg::kEpiCols < p.N) &&
                             !(kDebug && (dbg & kDebugSkipStores));
           if (live) {
             // The staging buffer about to be rewritten must have been read by its store.
@@ -831,13 +879,19 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           finish_chunk(cg, a0, a1);
           finish_chunk(cg + kColGroups, b0, b1);
         } else {
+          if (cg >= chunks_h) {
+            // a narrow tile leaves this warp without a chunk: it only hands the slot back
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8u * slot);
+          }
 #pragma unroll 1
-          for (int c = cg; c < kChunks; c += kColGroups) {
+          for (int c = cg; c < chunks_h; c += kColGroups) {
             uint32_t v0[32], v1[32];
             tmem_ld_32x32(taddr + c * Cfg::kEpiCols, v0);
             tmem_ld_32x32(taddr + c * Cfg::kEpiCols + 32, v1);
             tmem_ld_wait();
-            if (c + kColGroups >= kChunks) {
+            if (c + kColGroups >= chunks_h) {
               // All of this warp's reads of the slot are done: hand it back to the MMA issuer.
               tc_fence_before_sync();
               __syncwarp();

@@ -220,6 +220,12 @@ std::string describe_config(int index) {
   return std::string(buf);
 }
 
+std::string describe_plan(int M, int N, int K, int dtype) {
+  char buf[384];
+  raise_for(gemm_sm100_describe_plan(M, N, K, dtype, buf, sizeof(buf)), 0, "describe_plan");
+  return std::string(buf);
+}
+
 PYBIND11_MODULE(_C, m) {
   m.def("gemm_tn_test", &gemm_tn_test, "GEMM transpose-normal test function", pybind11::arg("A"),
         pybind11::arg("B"), pybind11::arg("C"));
@@ -237,6 +243,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("set_option", &set_option, pybind11::arg("name"), pybind11::arg("value"));
   m.def("set_trace_buffer", &set_trace_buffer, pybind11::arg("buffer"));
   m.def("describe_config", &describe_config, pybind11::arg("index"));
+  m.def("describe_plan", &describe_plan, pybind11::arg("M"), pybind11::arg("N"), pybind11::arg("K"),
+        pybind11::arg("dtype"));
   m.def("select_config", &gemm_sm100_select_config, pybind11::arg("M"), pybind11::arg("N"),
         pybind11::arg("K"), pybind11::arg("dtype"));
   m.def("workspace_bytes", &gemm_sm100_workspace_bytes, pybind11::arg("M"), pybind11::arg("N"),

@@ -34,6 +34,7 @@ init = _C.init
 set_option = _C.set_option
 set_trace_buffer = _C.set_trace_buffer
 describe_config = _C.describe_config
+describe_plan = _C.describe_plan
 select_config = _C.select_config
 workspace_bytes = _C.workspace_bytes
 num_sms = _C.num_sms
@@ -159,5 +160,5 @@ from .nsplit import FusedNSplit, NSplitPlan, fanout_pointers, gemm_tn_nsplit, sh
 
 __all__ = [
     "gemm_tn_test", "gemm_tn", "gemm_nn", "gemm", "HostGemm", "gemm_tn_fanout", "gemm_tn_nsplit", "FusedNSplit", "NSplitPlan", "shard_rows", "device_status",
-    "init", "set_option", "set_trace_buffer", "trace_launch", "describe_config", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
+    "init", "set_option", "set_trace_buffer", "trace_launch", "describe_config", "describe_plan", "select_config", "workspace_bytes", "num_sms", "LIBRARY_PATH",
 ]

@@ -104,7 +104,7 @@ def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     return rec
 
 
-OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": 0, "max_ctas": 0}
+OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0}
 
 KSPLIT_SHAPES = ("512x4096x4096,1024x4096x4096,256x8192x8192,256x512x65536,512x512x32768,1024x1024x16384,"
                  "2048x2048x8192,1024x2048x8192,512x4096x8192,128x2048x16384,256x256x32768,1024x1024x4096,"
@@ -184,8 +184,11 @@ def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None):
             for _ in range(3):
                 fn()
         torch.cuda.synchronize()
-        for _ in range(rounds):
-            for k, (settings, fn) in calls.items():
+        order = list(calls.items())
+        for r in range(rounds):
+            # every round starts at another variant: what a variant inherits from its predecessor
+            # (clock state, L2 contents) then averages out instead of sticking to one of them
+            for k, (settings, fn) in order[r % len(order):] + order[:r % len(order)]:
                 apply_options(settings)
                 res[k].append(timed(fn, n_iters, scratch))
         apply_options({})
@@ -196,7 +199,7 @@ def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None):
                "auto": gk.describe_config(gk.select_config(M, N, K, gk.DTYPE_CODES[dtype])),
                "auto_workspace_bytes": gk.workspace_bytes(M, N, K, gk.DTYPE_CODES[dtype]),
                "us": {k: round(statistics.median(v), 2) for k, v in res.items()},
-               "ratio_to_first": {k: round(statistics.median(a / b for a, b in zip(v, res[first])), 4)
+               "ratio_to_first": {k: round(statistics.median(v) / statistics.median(res[first]), 4)
                                   for k, v in res.items()},
                "tflops": {k: round(2.0 * M * N * K / statistics.median(v) / 1e6, 1) for k, v in res.items()},
                "gbs": {k: round(2.0 * (M * K + N * K + M * N) / statistics.median(v) / 1e3, 1) for k, v in res.items()}}

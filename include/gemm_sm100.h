@@ -167,11 +167,17 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  *                  pair, whenever the chosen configuration has a K-split variant; 2..8 = every
  *                  tile cut into that many equal K ranges with the reduction spread over the
  *                  contributors (256 x 256 and 128 x 256 tiles).
+ *   "balance"      1 = the planner may give a tile row a number of tiles that fills the SMs evenly,
+ *                  with tile widths in steps of 64 columns (default); 0 = uniform tiles only.
+ *   "tiles_n"      0 = the planner's choice (default); > 0 forces that many tiles per tile row
+ *                  (tests; ignored where the configuration cannot make tiles of the resulting widths).
  *   "group_m"      0 = default; tile rows per rasterisation group.
- *   "k_rotate"     order of a tile's K blocks: 0 = ascending (default); 1 = every tile starts at a
- *                  different K block and wraps; -1 = that, for a single tile row only; 2 = every
- *                  other tile of a CTA runs K backwards (re-reads the shared operand panel
- *                  newest-first).
+ *   "k_rotate"     order of a tile's K blocks: 0 = ascending; 1 = every tile starts at a different K
+ *                  block and wraps; -1 = that, for problems of at most 128 rows and at least 2048
+ *                  columns only (default: the CTAs of these memory-bound shapes then stream
+ *                  different column offsets of B at any moment; every other problem sums K in
+ *                  ascending order, so a row's result does not depend on how the caller cuts M); 2 = every other tile of a CTA runs K backwards (re-reads the
+ *                  shared operand panel newest-first).
  *   "debug_flags"  EXPERIMENTS ONLY, results are garbage while it is non-zero: bit 0 skips the
  *                  operand loads, bit 1 the stores of C, bit 2 the MMAs (pure issue-rate and
  *                  load-rate measurements of tests/trace_report.py).  Default 0.
@@ -184,6 +190,11 @@ int gemm_sm100_set_option(const char* name, long value);
 /* Writes a short description of tile configuration `index` ("cta_group=2 tile=256x256x64
  * stages=6 ...") into buf; returns GEMM_SM100_ERR_BAD_OPTION past the last index. */
 int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes);
+
+/* Writes what gemm_sm100_tn would do for this problem on the current device, in words: tile
+ * configuration, column tiling (uniform, or balanced with the tile widths), K-split schedule,
+ * grid size and workspace bytes.  For logs and benchmark records. */
+int gemm_sm100_describe_plan(int M, int N, int K, int dtype, char* buf, size_t buf_bytes);
 
 /* Index of the tile configuration gemm_sm100_tn would pick for this problem on the current
  * device (negative on error). */

@@ -69,6 +69,8 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_set_option.restype = I
     lib.gemm_sm100_describe_config.argtypes = [I, ctypes.c_char_p, Z]
     lib.gemm_sm100_describe_config.restype = I
+    lib.gemm_sm100_describe_plan.argtypes = [I, I, I, I, ctypes.c_char_p, Z]
+    lib.gemm_sm100_describe_plan.restype = I
     lib.gemm_sm100_select_config.argtypes = [I, I, I, I]
     lib.gemm_sm100_select_config.restype = I
     lib.gemm_sm100_selftest_wait_timeout.argtypes = [P, ctypes.POINTER(I)]

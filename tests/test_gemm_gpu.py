@@ -38,8 +38,10 @@ def _reset_options(capi):
     capi.gemm_sm100_set_option(b"tile_config", -1)
     capi.gemm_sm100_set_option(b"max_ctas", 0)
     capi.gemm_sm100_set_option(b"split_k", -1)
-    capi.gemm_sm100_set_option(b"k_rotate", 0)
+    capi.gemm_sm100_set_option(b"k_rotate", -1)
     capi.gemm_sm100_set_option(b"group_m", 0)
+    capi.gemm_sm100_set_option(b"tiles_n", 0)
+    capi.gemm_sm100_set_option(b"balance", 1)
 
 
 def run_capi(capi, A, B, prefill=float("nan")):
@@ -652,6 +654,69 @@ def test_tile_256x192_covers_ragged_columns(capi):
         B = ((torch.arange(N).view(N, 1) * 3 + torch.arange(K).view(1, K)) % 251).to(torch.bfloat16)
         C = run_capi(capi, A, B)
         assert torch.equal(C.view(torch.int16), B[:, ks].T.contiguous().view(torch.int16))
+
+
+def plan_text(capi, M, N, K):
+    buf = ctypes.create_string_buffer(384)
+    assert capi.gemm_sm100_describe_plan(M, N, K, 0, buf, 384) == 0
+    return buf.value.decode()
+
+
+# config, N, tiles per row: widths 64..256 (single-width tiles) and 320..512 (double-width), with and
+# without a remainder, ragged N (not a multiple of 64, not a multiple of 8 inside a wider buffer)
+BALANCED = [
+    (0, 1024, 5), (0, 1000, 5), (0, 2048 + 64, 11), (0, 4096, 21),
+    (1, 4096, 9), (1, 4096, 12), (1, 2048 + 320, 5), (1, 3000, 7), (1, 4096 + 8, 10),
+    (2, 1024, 5), (2, 2048 - 24, 10), (2, 28672 // 8, 17), (2, 640, 3),
+]
+
+
+@pytest.mark.parametrize("config,N,tiles_n", BALANCED)
+@pytest.mark.parametrize("max_ctas", [0, 6])
+def test_balanced_column_tiling(capi, config, N, tiles_n, max_ctas):
+    """Tile rows cut into a forced number of tiles of unequal width (multiples of 64 columns): a
+    one-hot A copies rows of a patterned B into C, so a tile that starts at the wrong column, an
+    MMA of the wrong width or a B box at the wrong row offset shows exactly; then seeded operands
+    inside the tolerance."""
+    M, K = 640, 192
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"tiles_n", tiles_n)
+    capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
+    assert f"balanced: {tiles_n} tiles per row" in plan_text(capi, M, N, K)
+    ks = (torch.arange(M) * 7) % K
+    A = torch.zeros(M, K, dtype=torch.bfloat16)
+    A[torch.arange(M), ks] = 1.0
+    B = ((torch.arange(N).view(N, 1) * 3 + torch.arange(K).view(1, K)) % 251).to(torch.bfloat16)
+    C = run_capi(capi, A, B)
+    assert torch.equal(C.view(torch.int16), B[:, ks].T.contiguous().view(torch.int16))
+    A2, B2 = oracle.make_inputs(M, N, K + 72, 210 + config)
+    assert_close(run_capi(capi, A2, B2), oracle.c_gemm_tn_f32(A2, B2), torch.bfloat16)
+
+
+def test_balanced_and_uniform_tilings_give_the_same_bits(capi):
+    """The column tiling only changes which CTA computes which columns: every element is the same
+    sum in the same K order, so the results must be identical."""
+    M, N, K = 1024, 4096, 1024
+    A, B = oracle.make_inputs(M, N, K, 214)
+    capi.gemm_sm100_set_option(b"tile_config", 1)
+    capi.gemm_sm100_set_option(b"balance", 0)
+    assert "uniform" in plan_text(capi, M, N, K)
+    uniform = run_capi(capi, A, B)
+    capi.gemm_sm100_set_option(b"balance", 1)
+    capi.gemm_sm100_set_option(b"tiles_n", 9)
+    assert "balanced: 9 tiles per row, 1 x 512 + 8 x 448" in plan_text(capi, M, N, K)
+    balanced = run_capi(capi, A, B)
+    assert torch.equal(uniform.view(torch.int16), balanced.view(torch.int16))
+    assert_close(balanced, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+
+
+def test_planner_balances_the_benchmark_shapes(capi):
+    """4096^3: 144 tiles of 448 / 512 columns on 74 CTA pairs instead of 128 tiles of 512; the
+    few-row shapes: one tile per SM."""
+    assert "balanced: 9 tiles per row, 1 x 512 + 8 x 448" in plan_text(capi, 4096, 4096, 4096)
+    assert "uniform: 112 tiles per row" in plan_text(capi, 16, 28672, 8192)
+    assert "uniform" in plan_text(capi, 8192, 8192, 8192)
+    assert "uniform" in plan_text(capi, 32768, 32768, 32768)
 
 
 def test_init_is_idempotent_and_later_launches_work(capi):
