@@ -258,17 +258,25 @@ int validate(const Problem& p) {
 
 inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 
-// Cost model used to choose a tile configuration: time ~ waves x (K blocks of a tile + what a tile
-// boundary costs) x tile columns / (relative rate of the configuration), where a wave is one tile
-// on every resident CTA (pair).  Fitted to interleaved timings of the configurations on B200
-// (power-capped steady state; 8192^3, 8192 x 8192 x {2048, 4096}, the two MLP shapes): the two pair
-// tiles run at the same rate within 1 %, and the 256 x 512 tile, whose accumulator fills TMEM,
-// loses about one K block per tile because its next tile cannot start before the accumulator is
-// drained.  So short K and bad wave counts go to the 256 x 256 tile, the rest to the wider one.
+// Cost model used to choose a tile configuration: time ~ longest chain of tiles on one CTA (pair) x
+// (K blocks of a tile + what a tile boundary costs) / (relative rate of the configuration).
+// Fitted to interleaved timings of the configurations on B200 (tests/gemm_bench.py --ab, variants
+// in rotating order; 8192^3, 8192 x 8192 x 4096, 16384^2 x 4096, 4096^3, 5120^3, the two MLP shapes):
+//  * The 256 x 512 tile, whose accumulator fills TMEM, loses about 2.5 K blocks per tile because its
+//    next tile cannot start before the accumulator is drained.
+//  * The 256 x 256 tile loads operands only 1.04x as fast as it computes (trace counters with the
+//    MMAs switched off; 1.27x for the 256 x 512 tile).  After an idle period, at the higher SM clock
+//    a GPU starts with, that margin is gone: 8192^3 in bursts of 20 launches took 790 us against
+//    718 us with the wide tile; in the power-capped steady state (lower SM clock, same L2) it was
+//    2-4 % faster than the wide tile.  The rate below sits between the two regimes.
+// So short K and chains that come out more than a few per cent longer go to the 256 x 256 tile, the
+// rest to the wider one.
 // Per configuration; rate 0 = not a candidate of the automatic choice (test / experiment variants).
 // The 256 x 128 pair tile (7) only matters when a problem has too few tiles for anything wider:
-// it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).
-constexpr double kConfigRate[kNumConfigs] = {0.99, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545, 0.955};
+// it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).  The
+// 256 x 192 tile (8) is load-bound (0.80x) and is kept for tests: balanced tilings of the two
+// 256-column configurations cover its use.
+constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545, 0.70};
 constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
 // in K blocks of that tile.
@@ -294,7 +302,7 @@ constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.
 struct Plan {
   int config = 0;
   // Column tiling (TileParams::bal_q / bal_rem): tiles_n tiles per tile row; 0 = uniform tiles.
-  int tiles_n = 0, bal_q = 0, bal_rem = 0;
+  int tiles_n = 0, bal_q = 0, bal_rem = 0, bal_start = 0;
   bool split_k = false;
   int ctas = 0;              // grid size
   size_t flag_bytes = 0;     // K-split: arrival counters (one per CTA), padded to 256 bytes
@@ -342,7 +350,7 @@ double effective_width(const ConfigInfo& c, int width) {
 
 // Longest chain of work any CTA (pair) gets under the static persistent schedule, for `tiles_n`
 // tiles per tile row dealt as the kernel deals them; in effective columns.
-double schedule_cost(const ConfigInfo& c, int m_tiles, int tiles_n, int q, int rem, long slots) {
+double schedule_cost(const ConfigInfo& c, int m_tiles, int tiles_n, int q, int rem, int start, long slots) {
   const long tiles = static_cast<long>(m_tiles) * tiles_n;
   const long clusters = tiles < slots ? tiles : slots;
   const int group_m = default_group_m(m_tiles);
@@ -351,7 +359,10 @@ double schedule_cost(const ConfigInfo& c, int m_tiles, int tiles_n, int q, int r
   for (long cl = 0; cl < clusters; ++cl) {
     double sum = 0.0;
     for (long t = cl; t < tiles; t += clusters)
-      sum += n_tile_of(t, m_tiles, tiles_n, group_m) < rem ? wide : narrow;
+    {
+      const int d = n_tile_of(t, m_tiles, tiles_n, group_m) - start;
+      sum += (d >= 0 && d < rem) ? wide : narrow;
+    }
     if (sum > worst) worst = sum;
   }
   return worst;
@@ -389,10 +400,11 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
       const int m_tiles = static_cast<int>(ceil_div(M, 128L * c.cta_group));
       const int chunks = static_cast<int>(ceil_div(N, 64));
       const int q_full = block_n / 64;
-      // double-width tiles keep both halves busy; single-width tiles narrower than 192 columns load
-      // more operand bytes per flop than the ring delivers (and few-tile problems are better off
-      // with the small-tile configurations and their deeper rings)
-      const int q_min = c.halves == 2 ? c.mma_n / 64 + 1 : 3;
+      // No MMA narrower than 192 columns: the 192-wide pair MMA still runs at the full tensor rate
+      // (0.99 in the trace counters with loads switched off), the 128-wide one does not, and
+      // few-tile problems are better off with the small-tile configurations and their deeper rings.
+      // So single-width tiles are 192 or 256 wide, double-width ones 448 or 512.
+      const int q_min = c.halves == 2 ? c.mma_n / 64 + 3 : 3;
       const int t_uniform = static_cast<int>(ceil_div(chunks, q_full));
       int t_last = chunks / q_min;
       if (t_last > 2 * t_uniform + 2) t_last = 2 * t_uniform + 2;
@@ -406,19 +418,25 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
         const int q = chunks / t_n, rem = chunks % t_n;
         if (forced_t > 0) {
           if (t_n <= chunks && q >= q_min && q + (rem ? 1 : 0) <= q_full) {
-            best_chain = schedule_cost(c, m_tiles, t_n, q, rem, slots);
-            cand.tiles_n = t_n, cand.bal_q = q, cand.bal_rem = rem;
+            best_chain = schedule_cost(c, m_tiles, t_n, q, rem, 0, slots);
+            cand.tiles_n = t_n, cand.bal_q = q, cand.bal_rem = rem, cand.bal_start = 0;
           }
           break;
         }
         if (q < q_min || q + (rem ? 1 : 0) > q_full) continue;
         if (static_cast<long>(m_tiles) * t_n > 40000) break;
-        const double chain = schedule_cost(c, m_tiles, t_n, q, rem, slots);
-        if (chain < best_chain * 0.98) {
-          best_chain = chain;
-          cand.tiles_n = t_n;
-          cand.bal_q = q;
-          cand.bal_rem = rem;
+        // where in the tile row the wider tiles sit decides which CTAs get two of them: first,
+        // middle or last, whichever leaves the shortest chain
+        const int starts[3] = {0, (t_n - rem) / 2, t_n - rem};
+        for (int si = 0; si < (rem ? 3 : 1); ++si) {
+          const double chain = schedule_cost(c, m_tiles, t_n, q, rem, starts[si], slots);
+          if (chain < best_chain * 0.98) {
+            best_chain = chain;
+            cand.tiles_n = t_n;
+            cand.bal_q = q;
+            cand.bal_rem = rem;
+            cand.bal_start = starts[si];
+          }
         }
       }
       if (cand.tiles_n > 0) {
@@ -548,6 +566,7 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.group_m = default_group_m(tp.m_tiles);
   tp.bal_q = Cfg::kBlockN / 64;
   tp.bal_rem = 0;
+  tp.bal_start = 0;
   tp.b_box_rows = Cfg::kBRows;
   tp.status = st.status_ptr;
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
@@ -563,6 +582,16 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.c_ptr = p.C;
   tp.ldc = p.ldc;
   return tp;
+}
+
+// Order of a tile's K blocks (TileParams::k_rotate) for this problem under the "k_rotate" option.
+// Automatic (-1): rotation only in the memory-bound few-row regime (at most 128 rows, thousands of
+// columns).  Other problems keep K ascending, so that the same rows give the same bits whether
+// they are computed in one call or in row panels, and in every operand layout.
+int k_order_for(const Problem& p, bool split_k) {
+  const long k_order = g_opt_k_rotate.load();
+  const bool few_rows = p.M <= 128 && p.N >= 2048 && !split_k;
+  return k_order == 2 ? 2 : ((k_order == 1 || (k_order < 0 && few_rows)) ? 1 : 0);
 }
 
 // Cluster launch of `kernel` on `ctas` CTAs of Cfg::kThreads threads.
@@ -666,16 +695,12 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
     tp.n_tiles = plan.tiles_n;
     tp.bal_q = plan.bal_q;
     tp.bal_rem = plan.bal_rem;
+    tp.bal_start = plan.bal_start;
     b_box = 64 / Cfg::kCtaGroup;          // tile widths are multiples of 64 columns: this CTA's share of them
     tp.b_box_rows = b_box;
   }
   tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
-  const long k_order = g_opt_k_rotate.load();
-  // Automatic (-1): only the memory-bound few-row regime (at most 128 rows, thousands of columns).
-  // Other problems keep K ascending, so that the same rows give the same bits whether they are
-  // computed in one call or in row panels.
-  const bool few_rows = p.M <= 128 && p.N >= 2048 && !plan.split_k;
-  tp.k_rotate = k_order == 2 ? 2 : ((k_order == 1 || (k_order < 0 && few_rows)) ? 1 : 0);
+  tp.k_rotate = k_order_for(p, plan.split_k);
   if (plan.split_k) {
     tp.sk_flags = static_cast<unsigned int*>(workspace);
     tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
@@ -756,7 +781,8 @@ int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t 
                           : (p.b_is_kn ? gemm_layout_kernel<Cfg, false, true> : gemm_layout_kernel<Cfg, false, false>);
   int rc = ensure_config<kCfgIndex, kIsBf16>(st, cuda_error_out);
   if (rc) return rc;
-  const TileParams tp = base_tile_params<Cfg>(p, st);
+  TileParams tp = base_tile_params<Cfg>(p, st);
+  tp.k_rotate = k_order_for(p, false);
   CUtensorMap map_a, map_b, map_c;
   rc = p.a_is_km ? encode_2d_cached(&map_a, p.A, p.dtype, p.K, p.M, p.lda, 64, cuda_error_out)   // K rows of M columns
                  : encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
@@ -1136,10 +1162,11 @@ int gemm_sm100_describe_plan(int M, int N, int K, int dtype, char* buf, size_t b
   const Plan plan = plan_for(M, N, K, current_sm_count());
   const ConfigInfo& c = kConfigs[plan.config];
   const int block_n = c.mma_n * c.halves;
-  char tiling[96];
+  char tiling[128];
   if (plan.tiles_n > 0)
-    std::snprintf(tiling, sizeof(tiling), "balanced: %d tiles per row, %d x %d + %d x %d columns", plan.tiles_n,
-                  plan.bal_rem, (plan.bal_q + 1) * 64, plan.tiles_n - plan.bal_rem, plan.bal_q * 64);
+    std::snprintf(tiling, sizeof(tiling), "balanced: %d tiles per row, %d x %d + %d x %d columns (wide from %d)",
+                  plan.tiles_n, plan.bal_rem, (plan.bal_q + 1) * 64, plan.tiles_n - plan.bal_rem, plan.bal_q * 64,
+                  plan.bal_start);
   else
     std::snprintf(tiling, sizeof(tiling), "uniform: %ld tiles per row of %d columns", ceil_div(N, block_n), block_n);
   char split[64];

@@ -60,13 +60,13 @@ struct TileParams {
   int k_blocks;  // ceil(K / 64)
   int group_m;   // tiles along M per rasterisation group
   // Column tiling.  The N / 64 chunks of 64 columns are dealt to the n_tiles tiles of a tile row:
-  // tile j covers (bal_q + (j < bal_rem)) chunks, starting at chunk j * bal_q + min(j, bal_rem).
+  // every tile covers bal_q chunks, the bal_rem tiles from index bal_start on one more.
   // Uniform tiles of kBlockN columns are bal_q = kBlockN / 64, bal_rem = 0 (the last tile hangs
   // over the edge: loads are zero-filled, stores clipped).  A balanced tiling gives the tile row
   // the number of tiles that fills the SMs evenly and makes the tiles as wide as that allows,
   // e.g. 4096 columns as 8 x 448 + 1 x 512 instead of 8 x 512.  Widths are at most kBlockN and,
   // for double-width configurations, more than kMmaN (both halves non-empty).
-  int bal_q, bal_rem;
+  int bal_q, bal_rem, bal_start;
   int b_box_rows;  // rows per TMA box of B: kBRows for uniform tiles, 64 / kCtaGroup for balanced ones
   unsigned int* status;            // device word, 0 = ok
   unsigned long long timeout_ns;   // bound of every device-side wait
@@ -318,10 +318,12 @@ struct TileCols {
 };
 template <class Cfg>
 __device__ __forceinline__ TileCols tile_columns(int n_tile, const TileParams& p) {
-  const bool wide = n_tile < p.bal_rem;
+  const int d = n_tile - p.bal_start;                      // wide tiles: d in [0, bal_rem)
+  const bool wide = d >= 0 && d < p.bal_rem;
+  const int wide_before = d <= 0 ? 0 : (d < p.bal_rem ? d : p.bal_rem);
   const int width = (p.bal_q + (wide ? 1 : 0)) * Cfg::kEpiCols;
   TileCols t;
-  t.col0 = (n_tile * p.bal_q + (wide ? n_tile : p.bal_rem)) * Cfg::kEpiCols;
+  t.col0 = (n_tile * p.bal_q + wide_before) * Cfg::kEpiCols;
   t.w0 = (Cfg::kHalves == 1 || width < Cfg::kMmaN) ? width : Cfg::kMmaN;
   t.w1 = width - t.w0;
   return t;

@@ -135,9 +135,16 @@ def apply_options(settings):
         gk.set_option(k, settings.get(k, v))
 
 
-def timed(fn, iters, scratch=None):
-    """µs per call: `iters` back-to-back calls between two events, or (with a scratch buffer)
-    single calls with an L2 flush before each, median."""
+def timed(fn, iters, scratch=None, cooldown=0.0):
+    """µs per call: `iters` back-to-back calls between two events (after `cooldown` seconds of idle
+    GPU, if given: a short burst then runs before the power cap reacts, as the first steps of a
+    benchmark do), or (with a scratch buffer) single calls with an L2 flush before each, median."""
+    if cooldown > 0.0:
+        import time
+
+        torch.cuda.synchronize()
+        time.sleep(cooldown)
+        fn()                                  # clocks up, instruction cache warm
     if scratch is None:
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
@@ -158,7 +165,7 @@ def timed(fn, iters, scratch=None):
     return statistics.median(times)
 
 
-def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None):
+def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None, cooldown=0.0):
     """Interleaved timing of option variants (and torch.mm) per shape; one JSON line per shape."""
     for (M, N, K) in shapes:
         A = (torch.randn((M, K), device="cuda") / K ** 0.5).to(dtype)
@@ -190,12 +197,12 @@ def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None):
             # (clock state, L2 contents) then averages out instead of sticking to one of them
             for k, (settings, fn) in order[r % len(order):] + order[:r % len(order)]:
                 apply_options(settings)
-                res[k].append(timed(fn, n_iters, scratch))
+                res[k].append(timed(fn, n_iters, scratch, cooldown))
         apply_options({})
         gk.device_status()
         first = next(iter(res))
         rec = {"M": M, "N": N, "K": K, "dtype": str(dtype).replace("torch.", ""), "rounds": rounds, "iters": n_iters,
-               "flush": scratch is not None,
+               "flush": scratch is not None, "cooldown_s": cooldown,
                "auto": gk.describe_config(gk.select_config(M, N, K, gk.DTYPE_CODES[dtype])),
                "auto_workspace_bytes": gk.workspace_bytes(M, N, K, gk.DTYPE_CODES[dtype]),
                "us": {k: round(statistics.median(v), 2) for k, v in res.items()},
@@ -219,6 +226,8 @@ def main():
     ap.add_argument("--rounds", type=int, default=6)
     ap.add_argument("--iters", type=int, default=0, help="launches per round (0 = about 20 ms worth)")
     ap.add_argument("--flush", action="store_true", help="A/B mode: single launches with an L2 flush before each")
+    ap.add_argument("--cooldown", type=float, default=0.0,
+                    help="A/B mode: idle seconds before every measurement (burst regime instead of the power-capped one)")
     ap.add_argument("--ksplit-table", action="store_true", help="A/B mode preset: K-split schedules on few-tile problems")
     ap.add_argument("--fanout", default=None, help="A/B mode on gemm_tn_fanout with these output counts (local buffers)")
     args = ap.parse_args()
@@ -233,7 +242,7 @@ def main():
         scratch = torch.zeros(512 * 1024 * 1024 // 4, dtype=torch.int32, device="cuda") if args.flush else None
         fanout = [int(x) for x in args.fanout.split(",")] if args.fanout else None
         print(f"device: {torch.cuda.get_device_name()}  SMs: {gk.num_sms()}")
-        ab_table(shapes, variants, dtype, args.rounds, args.iters, scratch, fanout)
+        ab_table(shapes, variants, dtype, args.rounds, args.iters, scratch, fanout, args.cooldown)
         return
     name, peak = peak_for_device()
     print(f"device: {torch.cuda.get_device_name()}  SMs: {gk.num_sms()}  nominal dense peak: {peak} TFLOP/s ({name})")

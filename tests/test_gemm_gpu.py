@@ -436,6 +436,9 @@ def test_nn_layout_matches_oracle(gk, capi, config, shape):
     A, Bt = oracle.make_inputs(M, N, K, 110 + M % 3)         # Bt is [N, K]
     B = Bt.T.contiguous()                                      # [K, N]
     capi.gemm_sm100_set_option(b"tile_config", config)
+    # K ascending in every tile: the automatic rotation of the few-row shapes starts each tile at a
+    # K block that depends on the tiling, and the two entry points may tile differently
+    capi.gemm_sm100_set_option(b"k_rotate", 0)
     C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
     out = gk.gemm_nn(A.cuda(), B.cuda(), C)
     gk.device_status()
@@ -666,7 +669,7 @@ def plan_text(capi, M, N, K):
 # without a remainder, ragged N (not a multiple of 64, not a multiple of 8 inside a wider buffer)
 BALANCED = [
     (0, 1024, 5), (0, 1000, 5), (0, 2048 + 64, 11), (0, 4096, 21),
-    (1, 4096, 9), (1, 4096, 12), (1, 2048 + 320, 5), (1, 3000, 7), (1, 4096 + 8, 10),
+    (1, 4096, 9), (1, 2048 + 320, 5), (1, 3136 - 24, 7), (1, 4096 + 8, 9), (1, 1024 - 8, 2),
     (2, 1024, 5), (2, 2048 - 24, 10), (2, 28672 // 8, 17), (2, 640, 3),
 ]
 
