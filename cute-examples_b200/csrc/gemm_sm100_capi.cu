@@ -36,10 +36,12 @@ constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 9;
+constexpr int kNumConfigs = 11;
 
 struct ConfigInfo {
   int cta_group, mma_n, halves, stages, epi_warps;
+  int a_rows = 128;    // rows of A loaded per stage: the configuration only takes problems of at most that many rows
+  int epi_bufs = 0;    // staging buffers per epilogue warp (0: 8 / epi_warps)
 };
 constexpr ConfigInfo kConfigs[kNumConfigs] = {
     {2, 256, 1, 6, 4},   // 256 x 256 pair tile, alternating accumulator slots
@@ -51,7 +53,16 @@ constexpr ConfigInfo kConfigs[kNumConfigs] = {
     {1, 256, 1, 4, 8},
     {2, 128, 1, 8, 4},   // 256 x 128 pair tile: fewest operand bytes per SM among the small tiles
     {2, 192, 1, 6, 4},   // 256 x 192 pair tile: for tile counts that quantise badly with 256 columns
+    // 128 x 256 tiles for problems of at most 16 / 64 rows: only those rows of A are loaded, and the
+    // shared memory saved holds more stages (6 / 5 x 32 KiB of B in flight per SM instead of 4)
+    {1, 256, 1, 6, 4, 16, 1},
+    {1, 256, 1, 5, 4, 64, 1},
 };
+
+template <int kIndex, bool kIsBf16>
+using ConfigOf = GemmConfig<kConfigs[kIndex].cta_group, kConfigs[kIndex].mma_n, kConfigs[kIndex].halves,
+                            kConfigs[kIndex].stages, kConfigs[kIndex].epi_warps, kIsBf16, kConfigs[kIndex].a_rows,
+                            kConfigs[kIndex].epi_bufs>;
 
 struct DeviceState {
   bool ready = false;
@@ -74,6 +85,7 @@ std::atomic<long> g_opt_max_ctas{0};
 std::atomic<long> g_opt_debug_flags{0};
 std::atomic<long> g_opt_group_m{0};
 std::atomic<long> g_opt_k_rotate{-1};   // 0 never, 1 always, -1 (default) when there is a single tile row: 3 % on the few-row shapes, 2 = serpentine
+std::atomic<long> g_opt_pdl{1};        // 1: launch with programmatic stream serialization (overlap with the previous kernel's tail)
 std::atomic<long> g_opt_tiles_n{0};    // > 0: force this many tiles per tile row (tests), when the configuration allows the widths
 std::atomic<long> g_opt_balance{1};    // 1: the planner may choose a balanced column tiling; 0: uniform tiles only
 std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
@@ -113,6 +125,7 @@ struct EnvOverrides {
     read("GEMM_SM100_GROUP_M", g_opt_group_m, 0, 4096);
     read("GEMM_SM100_MAX_CTAS", g_opt_max_ctas, 0, 1 << 20);
     read("GEMM_SM100_TIMEOUT_MS", g_opt_timeout_ms, 1, 60000);
+    read("GEMM_SM100_PDL", g_opt_pdl, 0, 1);
   }
 };
 const EnvOverrides g_env_overrides;
@@ -276,8 +289,8 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).  The
 // 256 x 192 tile (8) is load-bound (0.80x) and is kept for tests: balanced tilings of the two
 // 256-column configurations cover its use.
-constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545, 0.70};
-constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0};
+constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.545, 0.70, 0.80, 0.76};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
 // in K blocks of that tile.
 constexpr double kFanoutKBlocksPerOutput = 12.0;
@@ -297,7 +310,7 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // configuration's tile: about 12 us measured on B200 (counters zeroed by a memset node, partial
 // tiles written, the wait for the other contributors, one tile's worth of partial data read back
 // and stored; little of it overlaps the next unit's main loop).
-constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 
 struct Plan {
   int config = 0;
@@ -375,11 +388,16 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
   Plan best;
   double best_cost = 1e300;
   const long k_blocks = ceil_div(K, 64);
-  const int first = (g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs) ? static_cast<int>(g_opt_tile_config) : 0;
-  const bool forced_config = g_opt_tile_config >= 0 && g_opt_tile_config < kNumConfigs;
+  // A forced configuration that cannot take this problem (more rows than its A tile holds) is
+  // ignored: the automatic choice runs instead.
+  const long forced_index = g_opt_tile_config.load();
+  const bool forced_config = forced_index >= 0 && forced_index < kNumConfigs && forced_index < config_limit &&
+                             (kConfigs[forced_index].a_rows >= 128 || M <= kConfigs[forced_index].a_rows);
+  const int first = forced_config ? static_cast<int>(forced_index) : 0;
   const int last = forced_config ? first + 1 : config_limit;   // config_limit: callers whose kernels exist for the first few configurations only
   for (int i = first; i < last; ++i) {
     const ConfigInfo& c = kConfigs[i];
+    if (c.a_rows < 128 && M > c.a_rows) continue;        // few-row configurations: only what their A tile holds
     const int block_n = c.mma_n * c.halves;
     const long tiles = ceil_div(M, 128L * c.cta_group) * ceil_div(N, block_n);
     const int cap = grid_cap(c, sm_count);
@@ -602,13 +620,26 @@ cudaError_t launch_kernel(Kernel kernel, long ctas, cudaStream_t stream, const A
   cfg.blockDim = dim3(Cfg::kThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
-  attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = Cfg::kCtaGroup;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  if (Cfg::kCtaGroup == 2) {                           // single-CTA tiles are launched without a cluster
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = Cfg::kCtaGroup;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (g_opt_pdl.load() != 0) {
+    // Programmatic dependent launch: this kernel's CTAs may be scheduled while the previous kernel
+    // of the stream drains (if that kernel allows it, as these kernels do at their start); they
+    // set up barriers and tensor memory and then wait for it to complete before touching global
+    // memory.  Back-to-back GEMMs lose a few microseconds less between launches.
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   cfg.attrs = attrs;
-  cfg.numAttrs = Cfg::kCtaGroup == 2 ? 1 : 0;          // single-CTA tiles are launched without a cluster
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
@@ -617,7 +648,7 @@ cudaError_t launch_kernel(Kernel kernel, long ctas, cudaStream_t stream, const A
 template <int kCfgIndex, bool kIsBf16>
 int ensure_config(DeviceState& st, int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
-  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  using Cfg = ConfigOf<kCfgIndex, kIsBf16>;
   constexpr int dt = kIsBf16 ? 0 : 1;
   std::lock_guard<std::mutex> lock(g_mutex);
   if (st.attr_set[kCfgIndex][dt]) return GEMM_SM100_OK;
@@ -675,7 +706,7 @@ template <int kCfgIndex, bool kIsBf16>
 int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceState& st, cudaStream_t stream,
                   int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
-  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  using Cfg = ConfigOf<kCfgIndex, kIsBf16>;
   constexpr int dt = kIsBf16 ? 0 : 1;
   int rc = ensure_config<kCfgIndex, kIsBf16>(st, cuda_error_out);
   if (rc) return rc;
@@ -711,7 +742,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   }
 
   CUtensorMap map_a, map_b, map_c;
-  rc = encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kBlockM, cuda_error_out);
+  rc = encode_2d_cached(&map_a, p.A, p.dtype, p.M, p.K, p.lda, Cfg::kARows, cuda_error_out);
   if (rc) return rc;
   rc = encode_2d_cached(&map_b, p.B, p.dtype, p.N, p.K, p.ldb, b_box, cuda_error_out);
   if (rc) return rc;
@@ -738,7 +769,7 @@ template <int kCfgIndex, bool kIsBf16>
 int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, DeviceState& st, cudaStream_t stream,
                   int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
-  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  using Cfg = ConfigOf<kCfgIndex, kIsBf16>;
   static_assert(has_fanout(kCfgIndex), "no store-to-every-output variant of this configuration");
   constexpr int dt = kIsBf16 ? 0 : 1;
   int rc = ensure_config<kCfgIndex, kIsBf16>(st, cuda_error_out);
@@ -775,7 +806,7 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
 template <int kCfgIndex, bool kIsBf16>
 int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t stream, int* cuda_error_out) {
   constexpr ConfigInfo ci = kConfigs[kCfgIndex];
-  using Cfg = GemmConfig<ci.cta_group, ci.mma_n, ci.halves, ci.stages, ci.epi_warps, kIsBf16>;
+  using Cfg = ConfigOf<kCfgIndex, kIsBf16>;
   static_assert(has_layouts(kCfgIndex), "no layout variants of this configuration");
   auto kernel = p.a_is_km ? (p.b_is_kn ? gemm_layout_kernel<Cfg, true, true> : gemm_layout_kernel<Cfg, true, false>)
                           : (p.b_is_kn ? gemm_layout_kernel<Cfg, false, true> : gemm_layout_kernel<Cfg, false, false>);
@@ -820,6 +851,8 @@ int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cuda
     case 6: return launch_config<6, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 7: return launch_config<7, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 8: return launch_config<8, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 9: return launch_config<9, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 10: return launch_config<10, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }
@@ -1102,6 +1135,11 @@ int gemm_sm100_set_option(const char* name, long value) {
     g_opt_split_k = value;
     return GEMM_SM100_OK;
   }
+  if (std::strcmp(name, "pdl") == 0) {
+    if (value < 0 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_pdl = value;
+    return GEMM_SM100_OK;
+  }
   if (std::strcmp(name, "tiles_n") == 0) {
     if (value < 0 || value > (1 << 20)) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_tiles_n = value;
@@ -1150,8 +1188,10 @@ int gemm_sm100_describe_config(int index, char* buf, size_t buf_bytes) {
   if (index < 0 || index >= kNumConfigs) return GEMM_SM100_ERR_BAD_OPTION;
   const ConfigInfo& c = kConfigs[index];
   const int tmem_cols = 2 * c.mma_n <= 128 ? 128 : (2 * c.mma_n <= 256 ? 256 : 512);
-  std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d epilogue_warps=%d",
-                c.cta_group, 128 * c.cta_group, c.mma_n * c.halves, c.stages, tmem_cols, c.epi_warps);
+  int n = std::snprintf(buf, buf_bytes, "cta_group=%d tile=%dx%dx64 stages=%d tmem_cols=%d epilogue_warps=%d",
+                        c.cta_group, 128 * c.cta_group, c.mma_n * c.halves, c.stages, tmem_cols, c.epi_warps);
+  if (c.a_rows != 128 && n > 0 && static_cast<size_t>(n) < buf_bytes)
+    std::snprintf(buf + n, buf_bytes - n, " a_rows=%d", c.a_rows);
   return GEMM_SM100_OK;
 }
 

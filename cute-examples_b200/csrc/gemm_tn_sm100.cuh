@@ -117,10 +117,17 @@ enum : int {
   kTraceWords = 16,
 };
 
-template <int kCtaGroup_, int kMmaN_, int kHalves_, int kStages_, int kEpiWarps_, bool kIsBf16_>
+template <int kCtaGroup_, int kMmaN_, int kHalves_, int kStages_, int kEpiWarps_, bool kIsBf16_, int kARows_ = 128,
+          int kEpiBufs_ = 0>
 struct GemmConfig {
   static constexpr int kCtaGroup = kCtaGroup_;
-  static constexpr int kBlockM = 128;              // rows of A (and of the accumulator) per CTA
+  static constexpr int kBlockM = 128;              // rows of the accumulator (and of the MMA's A operand) per CTA
+  // Rows of A that are actually loaded per stage.  Less than 128 only in the configurations for
+  // problems of at most that many rows (M <= kARows): the MMA still reads a 128-row operand from
+  // the stage's address, and what lies behind the loaded rows (later stages of the ring) is
+  // multiplied into accumulator rows >= M, which nothing ever reads.  The shared memory saved
+  // goes into more stages: for the memory-bound few-row shapes, more of B in flight per SM.
+  static constexpr int kARows = kARows_;
   static constexpr int kMmaN = kMmaN_;             // N of one MMA instruction (whole pair)
   // kHalves == 1: the tile is kMmaN wide and the two accumulator slots in TMEM alternate
   //               between consecutive tiles (the epilogue of one runs under the next mainloop).
@@ -135,13 +142,13 @@ struct GemmConfig {
   static constexpr bool kIsBf16 = kIsBf16_;
   static constexpr int kUmmaK = 16;
   static constexpr int kBRows = kMmaN / kCtaGroup;              // rows of B this CTA loads per half
-  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kABytes = kARows * kBlockK * 2;
   static constexpr int kBHalfBytes = kBRows * kBlockK * 2;
   static constexpr int kBBytes = kHalves * kBHalfBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiCols = 64;                           // columns per TMA-store chunk
   static constexpr int kEpiWarpBuf = 32 * kEpiCols * 2;         // one warp, one chunk: 4 KiB
-  static constexpr int kEpiBufs = 8 / kEpiWarps;                // staging buffers per warp
+  static constexpr int kEpiBufs = kEpiBufs_ > 0 ? kEpiBufs_ : 8 / kEpiWarps;   // staging buffers per warp
   static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiWarpBuf;   // 32 KiB
   // Two accumulator slots.  TMEM is allocated in powers of two (32..512 columns); the slots sit
   // half an allocation apart, so a 192-column accumulator leaves 64 unused columns behind it.
@@ -156,6 +163,11 @@ struct GemmConfig {
   static_assert(kMmaN <= kSlotCols, "an accumulator must fit its slot");
   static_assert(kCtaGroup == 1 || kMmaN % 32 == 0, "pair MMA: each CTA supplies N / 2 rows of B, a multiple of 16");
   static_assert(kBHalfBytes % 1024 == 0, "B tile must keep 1024-byte swizzle alignment");
+  static_assert(kARows % 8 == 0 && kARows >= 8 && kARows <= kBlockM, "A rows: whole 8-row swizzle groups");
+  static_assert(kARows == kBlockM || kCtaGroup == 1, "short A tiles: single-CTA configurations only");
+  static_assert(kEpiBufs == 1 || kEpiBufs == 2, "staging buffers per epilogue warp");
+  // the MMA reads 128 rows from every A stage: the last stage's read must stay inside the ring
+  static_assert(kStages * kABytes + kBlockM * kBlockK * 2 - kABytes <= kStages * kStageBytes, "A over-read leaves the ring");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
@@ -372,6 +384,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     }
   }
 
+  // The next kernel in the stream (if it was launched for it) may be scheduled from now on: its
+  // CTAs take the SMs this grid leaves idle or frees, set themselves up and wait below.
+  grid_launch_dependents();
+
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;          // 128B-swizzle atoms need 1024 B
@@ -442,6 +458,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       if (warp == 1 && !is_leader && lane == 0) mbar_arrive_cluster(map_to_cta(bar_base + kTmemReadyOff, 0u));
     }
   }
+
+  // Everything up to here used only this CTA's own resources.  Global memory (operands that the
+  // previous kernel in the stream may have written, C that it may still be writing) comes next.
+  grid_dependency_wait();
 
   const int num_tiles = p.m_tiles * p.n_tiles;
   const int cluster_id = blockIdx.x / G;

@@ -59,6 +59,19 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// ------------------------------------------- programmatic dependent launch ---
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running, once every CTA of that kernel has executed
+// launch_dependents (or exited).  It must execute grid_dependency_wait before it touches global
+// memory: that returns when the earlier kernel has completed and its writes are visible.
+// Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // --------------------------------------------------------------- mbarrier ---
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -104,7 +104,7 @@ def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     return rec
 
 
-OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0}
+OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0, "pdl": 1}
 
 KSPLIT_SHAPES = ("512x4096x4096,1024x4096x4096,256x8192x8192,256x512x65536,512x512x32768,1024x1024x16384,"
                  "2048x2048x8192,1024x2048x8192,512x4096x8192,128x2048x16384,256x256x32768,1024x1024x4096,"
@@ -206,12 +206,13 @@ def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None, coold
                "auto": gk.describe_config(gk.select_config(M, N, K, gk.DTYPE_CODES[dtype])),
                "auto_workspace_bytes": gk.workspace_bytes(M, N, K, gk.DTYPE_CODES[dtype]),
                "us": {k: round(statistics.median(v), 2) for k, v in res.items()},
+               "min_us": {k: round(min(v), 2) for k, v in res.items()},
                "ratio_to_first": {k: round(statistics.median(v) / statistics.median(res[first]), 4)
                                   for k, v in res.items()},
                "tflops": {k: round(2.0 * M * N * K / statistics.median(v) / 1e6, 1) for k, v in res.items()},
                "gbs": {k: round(2.0 * (M * K + N * K + M * N) / statistics.median(v) / 1e3, 1) for k, v in res.items()}}
-        print(f"{M}x{N}x{K}: " + "  ".join(f"{k} {rec['us'][k]:.1f}us (x{rec['ratio_to_first'][k]:.3f})" for k in res),
-              flush=True)
+        print(f"{M}x{N}x{K}: " + "  ".join(f"{k} {rec['us'][k]:.1f}us (x{rec['ratio_to_first'][k]:.3f}, min "
+                                            f"{rec['min_us'][k]:.1f})" for k in res), flush=True)
         print(json.dumps(rec), flush=True)
         del A, B, C, outs
 

@@ -169,6 +169,11 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  *                  contributors (256 x 256 and 128 x 256 tiles).
  *   "balance"      1 = the planner may give a tile row a number of tiles that fills the SMs evenly,
  *                  with tile widths in steps of 64 columns (default); 0 = uniform tiles only.
+ *   "pdl"          1 = launch with the programmatic-stream-serialization attribute (default): when
+ *                  the previous kernel in the stream is one of this library's, the new kernel's
+ *                  CTAs are scheduled while it drains, set up their barriers and tensor memory,
+ *                  and wait for its completion before they touch global memory; after any other
+ *                  kernel the launch is an ordinary one.  0 = ordinary launches only.
  *   "tiles_n"      0 = the planner's choice (default); > 0 forces that many tiles per tile row
  *                  (tests; ignored where the configuration cannot make tiles of the resulting widths).
  *   "group_m"      0 = default; tile rows per rasterisation group.
@@ -182,7 +187,7 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  *                  operand loads, bit 1 the stores of C, bit 2 the MMAs (pure issue-rate and
  *                  load-rate measurements of tests/trace_report.py).  Default 0.
  * The environment variables GEMM_SM100_TILE_CONFIG, GEMM_SM100_SPLIT_K, GEMM_SM100_GROUP_M,
- * GEMM_SM100_MAX_CTAS and GEMM_SM100_TIMEOUT_MS give the initial values when the library is
+ * GEMM_SM100_MAX_CTAS, GEMM_SM100_TIMEOUT_MS and GEMM_SM100_PDL give the initial values when the library is
  * loaded ("debug_flags" has no variable on purpose).
  * The reference's equivalents are compile-time constants (gemm.cuh:420-451). */
 int gemm_sm100_set_option(const char* name, long value);

@@ -20,7 +20,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 DT = {0: torch.bfloat16, 1: torch.float16}
-NUM_CONFIGS = 9
+NUM_CONFIGS = 11
 
 
 @pytest.fixture(scope="module")
@@ -42,6 +42,7 @@ def _reset_options(capi):
     capi.gemm_sm100_set_option(b"group_m", 0)
     capi.gemm_sm100_set_option(b"tiles_n", 0)
     capi.gemm_sm100_set_option(b"balance", 1)
+    capi.gemm_sm100_set_option(b"pdl", 1)
 
 
 def run_capi(capi, A, B, prefill=float("nan")):
@@ -659,6 +660,47 @@ def test_tile_256x192_covers_ragged_columns(capi):
         assert torch.equal(C.view(torch.int16), B[:, ks].T.contiguous().view(torch.int16))
 
 
+@pytest.mark.parametrize("config,M", [(9, 1), (9, 8), (9, 16), (10, 17), (10, 40), (10, 64)])
+@pytest.mark.parametrize("N,K", [(1000, 2056), (3584, 512), (264, 64)])
+def test_short_a_tile_configurations(capi, config, M, N, K):
+    """The few-row configurations load only 16 / 64 rows of A per stage; the MMA's other operand rows
+    are whatever follows in the ring and land in accumulator rows nobody reads.  C sits inside a
+    sentinel-filled buffer: rows below and above it must stay untouched, the live rows exact
+    (ternary operands) and inside the tolerance (seeded operands)."""
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    assert f"config={config} " in plan_text(capi, M, N, K)
+    pad, ldc = 8, (N + 7) // 8 * 8 + 64
+    for ternary in (True, False):
+        A, B = (oracle.make_ternary_inputs(M, N, min(K, 256), 220) if ternary
+                else oracle.make_inputs(M, N, K, 221, a_std=1.0, b_std=0.02))
+        sentinel = -4321.0
+        buf = torch.full((M + 2 * pad, ldc), sentinel, dtype=torch.bfloat16, device="cuda")
+        C = buf[pad:pad + M, 32:32 + N]
+        assert capi_gemm(capi, A.cuda(), B.cuda(), C, ldc=ldc) == 0
+        assert capi_status(capi) == (0, 0)
+        host = buf.cpu()
+        got = host[pad:pad + M, 32:32 + N].clone()
+        if ternary:
+            assert torch.equal(got.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
+        else:
+            assert_close(got, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+        host[pad:pad + M, 32:32 + N] = sentinel
+        assert torch.all(host == sentinel), "kernel wrote outside C"
+
+
+def test_short_a_tile_configurations_refuse_taller_problems(capi):
+    """Forcing a few-row configuration on a problem with more rows than it loads falls back to the
+    automatic choice instead of computing garbage."""
+    capi.gemm_sm100_set_option(b"tile_config", 9)
+    assert "config=9 " not in plan_text(capi, 17, 4096, 1024)
+    A, B = oracle.make_inputs(100, 520, 264, 222)
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    capi.gemm_sm100_set_option(b"tile_config", -1)
+    assert "config=9 " in plan_text(capi, 16, 28672, 8192)
+    assert "config=10 " in plan_text(capi, 64, 28672, 8192)
+    assert "config=2 " in plan_text(capi, 128, 28672, 8192)
+
+
 def plan_text(capi, M, N, K):
     buf = ctypes.create_string_buffer(384)
     assert capi.gemm_sm100_describe_plan(M, N, K, 0, buf, 384) == 0
@@ -720,6 +762,31 @@ def test_planner_balances_the_benchmark_shapes(capi):
     assert "uniform: 112 tiles per row" in plan_text(capi, 16, 28672, 8192)
     assert "uniform" in plan_text(capi, 8192, 8192, 8192)
     assert "uniform" in plan_text(capi, 32768, 32768, 32768)
+
+
+def test_programmatic_launch_chain_keeps_order(gk, capi):
+    """Back-to-back launches that depend on each other through memory (the second multiplies the
+    first one's output), with and without programmatic dependent launch: the later kernel's early
+    start must not let it read or overwrite anything before the earlier one has finished."""
+    M = N = K = 512
+    A, B = oracle.make_ternary_inputs(M, N, K // 2, 230)
+    A = torch.cat([A, torch.zeros(M, K // 2, dtype=A.dtype)], dim=1)
+    B = torch.cat([B, torch.zeros(N, K // 2, dtype=B.dtype)], dim=1)
+    eye = torch.eye(N, dtype=torch.bfloat16, device="cuda")
+    want = oracle.c_gemm_tn(A, B)
+    for pdl in (1, 0):
+        capi.gemm_sm100_set_option(b"pdl", pdl)
+        Ad, Bd = A.cuda(), B.cuda()
+        C1 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        C2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        for _ in range(20):
+            gk.gemm_tn_test(Ad, Bd, C1)          # C1 = A B^T
+            gk.gemm_tn_test(C1, eye, C2)         # C2 = C1 I  (reads what the launch before wrote)
+            gk.gemm_tn_test(C2, eye, C1)         # C1 = C2 I  (overwrites what the launch before read)
+        gk.device_status()
+        assert torch.equal(C1.cpu().view(torch.int16), want.view(torch.int16))
+        assert torch.equal(C2.cpu().view(torch.int16), want.view(torch.int16))
+    capi.gemm_sm100_set_option(b"pdl", 1)
 
 
 def test_init_is_idempotent_and_later_launches_work(capi):
