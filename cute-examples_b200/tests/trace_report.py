@@ -38,6 +38,7 @@ def run(M, N, K, config, flags, warm=3):
     B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
     C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     gk.set_option("tile_config", config)
+    gk.set_option("balance", 0)              # uniform tiles: the ideal cycle count below assumes them
     gk.set_option("debug_flags", flags)
     trace = torch.zeros(gk.num_sms() * WORDS, dtype=torch.int64, device="cuda")
     try:
@@ -53,6 +54,7 @@ def run(M, N, K, config, flags, warm=3):
         gk.set_trace_buffer(None)
         gk.set_option("debug_flags", 0)
         gk.set_option("tile_config", -1)
+        gk.set_option("balance", 1)
     gk.device_status()
     return trace.cpu().numpy().reshape(-1, WORDS).astype(np.float64), start.elapsed_time(end)
 
@@ -74,6 +76,17 @@ def report(M, N, K, config, flags):
           f"set-up {np.mean(t[:, SETUP] - t[:, ENTRY]):.0f} cycles; first operand stage {np.mean(lead[:, MMA_FIRST] - lead[:, ENTRY]):.0f} cycles after entry")
     print(f"    ideal tensor cycles / MMA loop cycles = {ideal.mean() / loop.mean():.3f} "
           f"(loop {loop.mean():.0f} cycles, whole kernel {np.mean(t[:, EXIT] - t[:, ENTRY]):.0f})")
+    # phases in microseconds of this launch's own clock, and how far apart the CTAs start and finish
+    us = lambda cycles: cycles / clock / 1e3  # noqa: E731
+    span = t[:, T1_NS].max() - t[:, T0_NS].min()
+    loops = lead[:, MMA_END] - lead[:, MMA_FIRST]
+    print(f"    phases: entry -> first operand stage {us(np.mean(lead[:, MMA_FIRST] - lead[:, ENTRY])):.2f} us, MMA loop "
+          f"{us(loops.mean()):.2f} us (fastest CTA {us(loops.min()):.2f}, slowest {us(loops.max()):.2f}), last MMA -> exit "
+          f"{us(np.mean(lead[:, EXIT] - lead[:, MMA_END])):.2f} us; first entry -> last exit {span / 1e3:.1f} us; CTAs enter within "
+          f"{(t[:, T0_NS].max() - t[:, T0_NS].min()) / 1e3:.1f} us and exit within {(t[:, T1_NS].max() - t[:, T1_NS].min()) / 1e3:.1f} us")
+    operand_bytes = 2.0 * (M * K + N * K)
+    print(f"    operand bytes / mean MMA loop time = {operand_bytes / (us(loops.mean()) * 1e-6) / 1e12:.2f} TB/s; "
+          f"/ first entry -> last exit = {operand_bytes / (span * 1e-9) / 1e12:.2f} TB/s (meaningful for memory-bound shapes)")
     print(f"    waits: MMA on operands {100 * (lead[:, MMA_STALL_FULL] / loop).mean():.1f} %, MMA on a free accumulator "
           f"{100 * (lead[:, MMA_STALL_ACC] / loop).mean():.1f} %, producer on free slots "
           f"{100 * (t[:, PROD_STALL] / np.maximum(1, t[:, PROD_END] - t[:, SETUP])).mean():.1f} %, epilogue on accumulators "
