@@ -678,6 +678,17 @@ int ensure_config(DeviceState& st, int* cuda_error_out) {
     }
   }
   int max_ctas = st.sm_count;
+  if (Cfg::kCtaGroup == 1) {
+    // Persistent grid of single CTAs: what the device can hold at once (one CTA per SM with this
+    // much shared memory).  The K-split schedules rely on the whole grid being resident.
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tn_kernel<Cfg, false>, Cfg::kThreads,
+                                                      Cfg::kSmemBytes);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    if (per_sm < 1) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
+    const long resident = static_cast<long>(per_sm) * st.sm_count;
+    if (resident < max_ctas) max_ctas = static_cast<int>(resident);
+  }
   if (Cfg::kCtaGroup == 2) {
     cudaLaunchConfig_t qc = {};
     qc.gridDim = dim3(st.sm_count - st.sm_count % 2);

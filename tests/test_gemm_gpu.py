@@ -827,6 +827,35 @@ def test_repeated_calls_reuse_cached_plans_and_maps(gk):
         assert_close(Cd.cpu(), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
 
 
+def test_host_cost_per_call_on_a_cached_shape(gk, capi):
+    """Host time of one call when the shape, the buffers and the options repeat: the plan and the
+    three tensor maps come out of the per-thread caches, so what is left is argument checks and the
+    launch itself.  Measured over 300 asynchronous calls (fewer than the launch queue holds), through
+    the C ABI and through the torch binding; the bound is loose, the figures are printed."""
+    import time
+
+    M = N = K = 256
+    A = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    err = ctypes.c_int(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0, None, 0, stream, ctypes.byref(err))
+    results = {}
+    for name, call in (("c_abi", lambda: capi.gemm_sm100_tn(*args)), ("binding", lambda: gk.gemm_tn_test(A, B, C))):
+        for _ in range(20):
+            call()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(300):
+            call()
+        results[name] = (time.perf_counter() - t0) / 300 * 1e6
+        torch.cuda.synchronize()
+    assert capi_status(capi) == (0, 0)
+    print(f"host microseconds per call: {results}")
+    assert results["c_abi"] < 25.0 and results["binding"] < 40.0
+
+
 def test_option_change_invalidates_cached_plan(capi):
     M, N, K = 1024, 1024, 512
     first = capi.gemm_sm100_select_config(M, N, K, 0)
