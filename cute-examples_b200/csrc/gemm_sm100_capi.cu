@@ -86,6 +86,7 @@ std::atomic<long> g_opt_debug_flags{0};
 std::atomic<long> g_opt_group_m{0};
 std::atomic<long> g_opt_k_rotate{-1};   // 0 never, 1 always, -1 (default) when there is a single tile row: 3 % on the few-row shapes, 2 = serpentine
 std::atomic<long> g_opt_pdl{1};        // 1: launch with programmatic stream serialization (overlap with the previous kernel's tail)
+std::atomic<long> g_opt_early_prefetch{1};   // with pdl: L2 prefetch of the first stages before waiting for the previous kernel
 std::atomic<long> g_opt_tiles_n{0};    // > 0: force this many tiles per tile row (tests), when the configuration allows the widths
 std::atomic<long> g_opt_balance{1};    // 1: the planner may choose a balanced column tiling; 0: uniform tiles only
 std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
@@ -586,6 +587,7 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.bal_rem = 0;
   tp.bal_start = 0;
   tp.b_box_rows = Cfg::kBRows;
+  tp.early_prefetch = (g_opt_pdl.load() != 0 && g_opt_early_prefetch.load() != 0) ? 1 : 0;
   tp.status = st.status_ptr;
   tp.timeout_ns = static_cast<unsigned long long>(g_opt_timeout_ms.load()) * 1000000ull;
   tp.trace = nullptr;
@@ -1149,6 +1151,11 @@ int gemm_sm100_set_option(const char* name, long value) {
   if (std::strcmp(name, "pdl") == 0) {
     if (value < 0 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_pdl = value;
+    return GEMM_SM100_OK;
+  }
+  if (std::strcmp(name, "early_prefetch") == 0) {
+    if (value < 0 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_early_prefetch = value;
     return GEMM_SM100_OK;
   }
   if (std::strcmp(name, "tiles_n") == 0) {

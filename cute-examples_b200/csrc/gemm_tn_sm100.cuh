@@ -68,6 +68,11 @@ struct TileParams {
   // for double-width configurations, more than kMmaN (both halves non-empty).
   int bal_q, bal_rem, bal_start;
   int b_box_rows;  // rows per TMA box of B: kBRows for uniform tiles, 64 / kCtaGroup for balanced ones
+  // > 0: before waiting for the previous kernel of the stream (programmatic dependent launch), the
+  // producer asks L2 for the operand boxes of its first ring of stages.  A prefetch is only a hint
+  // and L2 is where this GPU's writes become visible, so it is safe whatever that kernel still
+  // writes; it puts the DRAM reads of this launch's first stages under that kernel's tail.
+  int early_prefetch;
   unsigned int* status;            // device word, 0 = ok
   unsigned long long timeout_ns;   // bound of every device-side wait
   unsigned long long* trace;       // optional: kTraceWords counters per CTA (nullptr = off)
@@ -459,15 +464,44 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     }
   }
 
-  // Everything up to here used only this CTA's own resources.  Global memory (operands that the
-  // previous kernel in the stream may have written, C that it may still be writing) comes next.
-  grid_dependency_wait();
-
   const int num_tiles = p.m_tiles * p.n_tiles;
   const int cluster_id = blockIdx.x / G;
   const int num_clusters = gridDim.x / G;
   const int k_blocks = p.k_blocks;
   const int sk_factor = (kSplitK && Cfg::kHalves == 1) ? p.sk_factor : 0;   // even split: single-width tiles only
+
+  if constexpr (!kSplitK && !kBIsKN && !kAIsKM) {
+    if (warp == 0 && p.early_prefetch > 0 && cluster_id < num_tiles) {
+      // L2 prefetch of the first tile's first kStages K blocks (the boxes the producer loads first)
+      if (elect_one()) {
+        int m_tile, n_tile;
+        tile_coords(cluster_id, p, m_tile, n_tile);
+        const TileCols tc = tile_columns<Cfg>(n_tile, p);
+        const int row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
+        const int rot = p.k_rotate == 1 ? (int)(((long long)cluster_id * k_blocks) / num_tiles) : 0;
+        const int stages = k_blocks < kStages ? k_blocks : kStages;
+        for (int kb = 0; kb < stages; ++kb) {
+          int kb_phys = kb + rot;
+          if (kb_phys >= k_blocks) kb_phys -= k_blocks;
+          const int x = kb_phys * Cfg::kBlockK;
+          if (row_a < p.M) tma_prefetch_2d(&tmap_a, x, row_a);
+#pragma unroll
+          for (int h = 0; h < Cfg::kHalves; ++h) {
+            const int rows = (h ? tc.w1 : tc.w0) / G;
+            const int row0 = tc.col0 + (h ? tc.w0 : 0) + (int)cta_rank * rows;
+            for (int j = 0; j < rows; j += p.b_box_rows)
+              if (row0 + j < p.N) tma_prefetch_2d(&tmap_b, x, row0 + j);
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+
+  // Everything up to here used only this CTA's own resources (and hints to L2).  Global memory
+  // (operands that the previous kernel in the stream may have written, C that it may still be
+  // writing) comes next.
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer

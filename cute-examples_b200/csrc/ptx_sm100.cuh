@@ -185,6 +185,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
   }
 }
 
+// Hint: bring the box at (x, y) into L2.  Nothing is written to shared memory and nothing
+// completes; the later load of the same box then finds its lines in L2.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+               : "memory");
+}
+
 // 2-D tiled store, shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int32_t x,
                                              int32_t y) {

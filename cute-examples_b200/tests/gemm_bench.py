@@ -104,7 +104,7 @@ def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     return rec
 
 
-OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0, "pdl": 1}
+OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0, "pdl": 1, "early_prefetch": 1}
 
 KSPLIT_SHAPES = ("512x4096x4096,1024x4096x4096,256x8192x8192,256x512x65536,512x512x32768,1024x1024x16384,"
                  "2048x2048x8192,1024x2048x8192,512x4096x8192,128x2048x16384,256x256x32768,1024x1024x4096,"

@@ -43,6 +43,7 @@ def _reset_options(capi):
     capi.gemm_sm100_set_option(b"tiles_n", 0)
     capi.gemm_sm100_set_option(b"balance", 1)
     capi.gemm_sm100_set_option(b"pdl", 1)
+    capi.gemm_sm100_set_option(b"early_prefetch", 1)
 
 
 def run_capi(capi, A, B, prefill=float("nan")):
@@ -774,8 +775,9 @@ def test_programmatic_launch_chain_keeps_order(gk, capi):
     B = torch.cat([B, torch.zeros(N, K // 2, dtype=B.dtype)], dim=1)
     eye = torch.eye(N, dtype=torch.bfloat16, device="cuda")
     want = oracle.c_gemm_tn(A, B)
-    for pdl in (1, 0):
+    for pdl, prefetch in ((1, 1), (1, 0), (0, 0)):
         capi.gemm_sm100_set_option(b"pdl", pdl)
+        capi.gemm_sm100_set_option(b"early_prefetch", prefetch)
         Ad, Bd = A.cuda(), B.cuda()
         C1 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
         C2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -787,6 +789,22 @@ def test_programmatic_launch_chain_keeps_order(gk, capi):
         assert torch.equal(C1.cpu().view(torch.int16), want.view(torch.int16))
         assert torch.equal(C2.cpu().view(torch.int16), want.view(torch.int16))
     capi.gemm_sm100_set_option(b"pdl", 1)
+    capi.gemm_sm100_set_option(b"early_prefetch", 1)
+
+
+@pytest.mark.parametrize("shape", [(16, 3584, 1024), (300, 1000, 72), (1024, 4096, 192), (8, 8, 8)])
+def test_early_prefetch_touches_nothing_out_of_range(capi, shape):
+    """The L2 prefetch before the dependency wait names the same boxes as the first loads; ragged
+    shapes (rows past M and N, fewer K blocks than stages) must neither fault nor change the result."""
+    M, N, K = shape
+    A, B = oracle.make_inputs(M, N, K, 231)
+    outs = []
+    for prefetch in (1, 0):
+        capi.gemm_sm100_set_option(b"early_prefetch", prefetch)
+        outs.append(run_capi(capi, A, B))
+    capi.gemm_sm100_set_option(b"early_prefetch", 1)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert_close(outs[0], oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
 
 
 def test_init_is_idempotent_and_later_launches_work(capi):
