@@ -5,7 +5,8 @@ Launched with one process per GPU:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 --master-port P \\
         cute-examples_b200/tests/nsplit_bench.py [--n 32768] [--variants fused,fused_c0,fused_c1,fused_1buf,nccl8,local,mm]
 
-Variants (timed in alternation, `--rounds` rounds of `--iters` steps, CUDA events, max over ranks):
+Variants (timed in alternation, every round starting at another variant, `--rounds` rounds of `--iters`
+steps, CUDA events, max over ranks):
     fused       FusedNSplit as the library configures it (two copies of C, one barrier per step)
     fused_c0    the same with the 256 x 256 pair tile forced;  fused_c1: the 256 x 512 tile forced
     fused_1buf  one copy of C, a barrier before and after the GEMM
@@ -139,8 +140,11 @@ def main():
     res = {k: [] for k in calls}
     for k, fn in calls.items():
         fn()
-    for _ in range(args.rounds):
-        for k, fn in calls.items():
+    order = list(calls.items())
+    for r in range(args.rounds):
+        # every round starts at another variant: in the power-capped state a variant inherits the
+        # temperature its predecessor left, and a fixed order would pin that on one of them
+        for k, fn in order[r % len(order):] + order[:r % len(order)]:
             res[k].append(timed(fn, args.iters))
     gk.device_status()
 
