@@ -86,18 +86,17 @@ def main():
         local_only = [ptrs[rank] + j * per * 2 for j in range(outs)]
         C_plain = torch.empty((M, per), dtype=dtype, device=device)
 
-        def fan(cfg, where):
+        def fan(where):
             def f():
-                gk.set_option("tile_config", cfg)
                 gk.gemm_tn_fanout(A, B_shard, where, outs * per)
-                gk.set_option("tile_config", -1)
                 handle.barrier(channel=1)
             return f
 
-        calls = {"peer_auto": fan(-1, targets), "peer_c0": fan(0, targets), "peer_c1": fan(1, targets),
-                 "local_c0": fan(0, local_only), "local_c1": fan(1, local_only),
-                 "plain": lambda: gk.gemm_tn_test(A, B_shard, C_plain),
-                 "mm": lambda: torch.mm(A, B_shard.T, out=C_plain)}
+        # variant -> (forced tile configuration or -1, step)
+        calls = {"peer_auto": (-1, fan(targets)), "peer_c0": (0, fan(targets)), "peer_c1": (1, fan(targets)),
+                 "local_c0": (0, fan(local_only)), "local_c1": (1, fan(local_only)),
+                 "plain": (-1, lambda: gk.gemm_tn_test(A, B_shard, C_plain)),
+                 "mm": (-1, lambda: torch.mm(A, B_shard.T, out=C_plain))}
     else:
         lo, hi = gk.shard_rows(N, world, rank)
         gb = torch.Generator(device=device).manual_seed(4000 + rank)
@@ -112,46 +111,42 @@ def main():
             C_full = torch.empty((M, N), dtype=dtype, device=device)
             plan8 = gk.NSplitPlan.create(M, N, world, dtype, device, num_panels=8)
 
-        def forced(obj, cfg):
-            def f():
-                gk.set_option("tile_config", cfg)
-                obj(A, B_shard)
-                gk.set_option("tile_config", -1)
-            return f
-
         for v in wanted:
             if v == "fused":
-                calls[v] = lambda: fused2(A, B_shard)
+                calls[v] = (-1, lambda: fused2(A, B_shard))
             elif v == "fused_c0":
-                calls[v] = forced(fused2, 0)
+                calls[v] = (0, lambda: fused2(A, B_shard))
             elif v == "fused_c1":
-                calls[v] = forced(fused2, 1)
+                calls[v] = (1, lambda: fused2(A, B_shard))
             elif v == "fused_1buf":
-                calls[v] = lambda: fused1(A, B_shard)
+                calls[v] = (-1, lambda: fused1(A, B_shard))
             elif v == "nccl8":
-                calls[v] = lambda: gk.gemm_tn_nsplit(A, B_shard, C_full, plan=plan8)
+                calls[v] = (-1, lambda: gk.gemm_tn_nsplit(A, B_shard, C_full, plan=plan8))
             elif v == "local":
-                calls[v] = lambda: gk.gemm_tn_test(A, B_shard, C_slab)
+                calls[v] = (-1, lambda: gk.gemm_tn_test(A, B_shard, C_slab))
             elif v == "mm":
-                calls[v] = lambda: torch.mm(A, B_shard.T, out=C_slab)
+                calls[v] = (-1, lambda: torch.mm(A, B_shard.T, out=C_slab))
             else:
                 raise SystemExit(f"unknown variant {v}")
 
     res = {k: [] for k in calls}
-    for k, fn in calls.items():
+    for k, (cfg, fn) in calls.items():
+        gk.set_option("tile_config", cfg)
         fn()
     order = list(calls.items())
     for r in range(args.rounds):
         # every round starts at another variant: in the power-capped state a variant inherits the
         # temperature its predecessor left, and a fixed order would pin that on one of them
-        for k, fn in order[r % len(order):] + order[:r % len(order)]:
+        for k, (cfg, fn) in order[r % len(order):] + order[:r % len(order)]:
+            gk.set_option("tile_config", cfg)          # once per measurement, not per step
             res[k].append(timed(fn, args.iters))
+    gk.set_option("tile_config", -1)
     gk.device_status()
 
     check = None
     if args.emulate_outputs:
         gk.gemm_tn_test(A, B_shard, C_plain)
-        calls["peer_auto"]()
+        calls["peer_auto"][1]()
         torch.cuda.synchronize()
         dist.barrier(device_ids=[local])
         # slab 0 of my buffer is my own product; slabs 1.. hold the previous rank's product
