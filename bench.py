@@ -428,6 +428,16 @@ def run_single(args):
     gk.device_status()
     e2e_tflops = gemm_flops(M, N, K) / e2e_ms / 1e9
     e2e_check = float((Ch[::1024].float() - C[::1024].cpu().float()).abs().max().item())
+
+    # what the upload alone costs on this box: the floor of the end-to-end step (the download of C
+    # and the GEMMs run under it)
+    def upload_only():
+        host_gemm.A.copy_(Ah, non_blocking=True)
+        host_gemm.B.copy_(Bh, non_blocking=True)
+
+    upload_only()
+    torch.cuda.synchronize()
+    h2d_floor_ms = time_steps(upload_only, 5, torch.cuda.synchronize) / 5
     del host_gemm
 
     del A, B, C, Ah, Bh, Ch
@@ -455,7 +465,10 @@ def run_single(args):
         "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
                 "api": "gemm_kernels.HostGemm (A uploaded in row panels; GEMM and download of C per panel)",
-                "max_abs_diff_vs_device_path": e2e_check},
+                "max_abs_diff_vs_device_path": e2e_check,
+                "upload_only_ms": round(h2d_floor_ms, 4),
+                "upload_only_note": "the same pinned A and B copied to the device with nothing else running: the floor "
+                                    "of the step on this box's PCIe link"},
         "gpu_launches": args.steps,
         "clocks": dict(clk.summary(), kernel_cycles=round(traced["cycles"]),
                        sm_mhz_effective=round(sm_mhz_effective),
@@ -583,17 +596,13 @@ def run_multi(args):
     mm_step = lambda: torch.mm(A, B_shard.T, out=C_mm)  # noqa: E731
     local_step()
     mm_step()
-    barrier()
-    torch.cuda.synchronize()
+    # Blocks of `steps` back-to-back launches, ours and cuBLAS in turn, twice: the same regime (power-
+    # capped, no idle gaps) as the fused step above.  Launches timed one by one with a synchronise in
+    # between would run cooler and faster and make the exchange look expensive.
     ours_ms, mm_ms = [], []
-    for _ in range(args.steps):
+    for _ in range(2):
         for fn, acc in ((local_step, ours_ms), (mm_step, mm_ms)):
-            s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s_ev.record()
-            fn()
-            e_ev.record()
-            e_ev.synchronize()
-            acc.append(s_ev.elapsed_time(e_ev))
+            acc.append(time_steps(fn, args.steps, torch.cuda.synchronize, barrier) / 2)
     gk.device_status()
     local_total, mm_total = sum(ours_ms), sum(mm_ms)
     t = torch.tensor([local_total, mm_total], dtype=torch.float64, device=device)
@@ -640,8 +649,9 @@ def run_multi(args):
             "parity": parity,
             "details": {"exchange": how, "nsplit_mode": mode, "per_gpu_tflops": round(per_gpu, 2),
                         "local_gemm_ms_per_step": round(local_ms, 4),
-                        "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange, timed "
-                                           "launch by launch in alternation with cuBLAS (torch.mm) on the same slab",
+                        "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange: blocks of "
+                                           "`steps` back-to-back launches, in turn with blocks of cuBLAS (torch.mm) "
+                                           "on the same slab, two blocks each",
                         "local_gemm_ms_per_rank": local_ms_per_rank,
                         "cublas_slab_ms_per_step": round(cublas_ms, 4),
                         "cublas_slab_ms_per_rank": cublas_ms_per_rank,
