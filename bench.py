@@ -306,10 +306,24 @@ def secondary_shapes(gk, peaks, device, with_cpu=True):
                 e.synchronize()
                 times.append(s.elapsed_time(e))
         ms = statistics.median(times)
+        ms_b2b = None
+        if bound == "tensor" and gemm_bytes(M, N, K) < 120e6:
+            # operands fit L2: also the warm figure, 20 launches back to back (launches then overlap
+            # with their predecessor's tail, which a flush kernel in between prevents)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(20):
+                gk.gemm_tn_test(A, B, C)
+            e.record()
+            e.synchronize()
+            ms_b2b = s.elapsed_time(e) / 20
         tf = gemm_flops(M, N, K) / ms / 1e9
         gbs = gemm_bytes(M, N, K) / ms / 1e6
         rec = {"shape": name, "ms": round(ms, 4), "tflops": round(tf, 1), "gbs": round(gbs, 1), "bound": bound,
                "l2": "inputs larger than L2, back to back" if bound == "hbm" else "flushed between iterations"}
+        if ms_b2b is not None:
+            rec["ms_back_to_back_warm_l2"] = round(ms_b2b, 4)
+            rec["tflops_back_to_back_warm_l2"] = round(gemm_flops(M, N, K) / ms_b2b / 1e9, 1)
         if bound == "tensor":
             rec["frac"] = round(tf / peaks["bf16_tflops"], 4)
         else:

@@ -30,6 +30,14 @@
 // boundary cuts.  The finished tile can be stored through several output tensor maps
 // (gemm_tn_fanout_kernel): that is how the column-sharded multi-GPU GEMM writes every GPU's C.
 //
+// The columns of a tile row need not be cut into equal tiles: tile widths are launch parameters in
+// steps of 64 columns (TileParams::bal_*), so the host can give a tile row the number of tiles that
+// fills the SMs evenly; the MMA's N, the B rows loaded and the epilogue's chunk count follow.
+//
+// Launch overlap: the kernel lets the next kernel of the stream be scheduled as soon as it starts
+// (griddepcontrol.launch_dependents), and itself waits for the previous kernel
+// (griddepcontrol.wait) only after its set-up, before its first access to global memory.
+//
 // Every wait is bounded: when one runs out the CTA (and its pair peer) is flagged, all roles
 // fall through to the common tear-down, TMEM is released and the launcher reports the status
 // word.  The reference's waits are unbounded (gemm.cuh:75-78, 91-94).

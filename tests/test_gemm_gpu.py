@@ -717,6 +717,28 @@ BALANCED = [
 ]
 
 
+@pytest.mark.parametrize("config,N,tiles_n", [(1, 4096, 9), (0, 2048 + 64, 11), (2, 640, 3)])
+def test_balanced_column_tiling_fp16_exact(capi, config, N, tiles_n):
+    """The same tilings with fp16 operands (the instruction descriptor's format bits and the
+    epilogue's conversion are the only differences): ternary operands, exact result."""
+    M, K = 520, 256
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"tiles_n", tiles_n)
+    A, B = oracle.make_ternary_inputs(M, N, K, 215, torch.float16)
+    C = run_capi(capi, A, B)
+    assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
+
+
+@pytest.mark.parametrize("config,M", [(9, 16), (10, 48)])
+def test_short_a_tile_configurations_fp16(capi, config, M):
+    N, K = 2048 + 8, 1024 + 64
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    A, B = oracle.make_inputs(M, N, K, 223, torch.float16, a_std=1.0, b_std=0.02)
+    assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.float16)
+    At, Bt = oracle.make_ternary_inputs(M, N, 256, 224, torch.float16)
+    assert torch.equal(run_capi(capi, At, Bt).view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
 @pytest.mark.parametrize("config,N,tiles_n", BALANCED)
 @pytest.mark.parametrize("max_ctas", [0, 6])
 def test_balanced_column_tiling(capi, config, N, tiles_n, max_ctas):
