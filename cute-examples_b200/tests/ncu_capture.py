@@ -13,11 +13,11 @@ Nsight by hand).  For a shape (or a named benchmark configuration) this script
      activity, DRAM bytes (read, write, per launch), DRAM and L2 throughput, L2 hit rate, stall
      reasons, registers, grid.
 
-Raw output goes to `--out` (default gpurun_out/); only the printed table is meant to be kept.
+Raw output goes to `--out` (default profile_out/); only the printed table is meant to be kept.
 
     python cute-examples_b200/tests/ncu_capture.py --config cfg2-8192
     python cute-examples_b200/tests/ncu_capture.py --m 4096 --n 4096 --k 4096 --tile-config 8 --metrics short
-    python cute-examples_b200/tests/ncu_capture.py --summarize gpurun_out/prof_8192x8192x8192_bf16.csv
+    python cute-examples_b200/tests/ncu_capture.py --summarize profile_out/prof_8192x8192x8192_bf16.csv
 """
 import argparse
 import csv
@@ -146,7 +146,7 @@ def main():
     ap.add_argument("--metrics", default="full", choices=["full", "short"],
                     help="full = --set full (about 40 passes per launch); short = a dozen metrics (a few passes)")
     ap.add_argument("--kernel", default="gemm_tn", help="regex of the kernel name to capture")
-    ap.add_argument("--out", default="gpurun_out")
+    ap.add_argument("--out", default="profile_out")
     ap.add_argument("--summarize", default=None, help="only print the table of an existing raw CSV")
     args = ap.parse_args()
 
