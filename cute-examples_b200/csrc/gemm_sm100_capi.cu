@@ -298,8 +298,12 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76};
 constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
-// in K blocks of that tile.
-constexpr double kFanoutKBlocksPerOutput = 12.0;
+// in K blocks of that tile.  Trace counters with all outputs in local memory (32768 x 4096 x 8192):
+// the MMA issuer's wait for a free accumulator grows from 2.6 % of the loop with one output to 6.4 %
+// with four and 10.8 % with eight, about 1.5 K blocks per output; with seven of eight outputs across
+// NVLink (two GPUs emulating the stores of an eight-GPU run, K = 32768) the wide tile lost 8-10 % against
+// the plain kernel and the 256 x 256 tile 2-5 %, about 6.5 K blocks per remote output.
+constexpr double kFanoutKBlocksPerOutput = 6.5;
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
 constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2; }
@@ -1006,8 +1010,7 @@ int gemm_sm100_tn_fanout(const void* A, const void* B, void* const* outputs, int
   // `num_outputs` destinations (all but one of them across NVLink in the multi-GPU use) is
   // exposed before the next tile's first MMA; the 256 x 256 tile drains one accumulator slot
   // while the tensor pipe fills the other, with two staging buffers per warp, and hides it.
-  // Measured on 8 GPUs (32768 x 4096 x 32768 slabs): 16 % of the step with the wide tile.  About
-  // one K block per output beyond the first, fitted to that.
+  // See kFanoutKBlocksPerOutput for the measurements behind the constant.
   const long slots = st->sm_count / 2;
   const double k_blocks = static_cast<double>(ceil_div(K, 64L));
   const double cost0 = static_cast<double>(ceil_div(ceil_div(M, 256L) * ceil_div(N, 256L), slots)) * 256 *

@@ -33,6 +33,9 @@ def describe(index):
     return text, int(fields["cta_group"]), tile_n
 
 
+FANOUT = 0   # > 0: trace the store-to-every-output kernel with this many outputs (all in local memory)
+
+
 def run(M, N, K, config, flags, warm=3):
     A = (torch.randn(M, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
     B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
@@ -41,13 +44,19 @@ def run(M, N, K, config, flags, warm=3):
     gk.set_option("balance", 0)              # uniform tiles: the ideal cycle count below assumes them
     gk.set_option("debug_flags", flags)
     trace = torch.zeros(gk.num_sms() * WORDS, dtype=torch.int64, device="cuda")
+    if FANOUT > 0:
+        outs = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(FANOUT)]
+        ptrs = [o.data_ptr() for o in outs]
+        launch = lambda: gk.gemm_tn_fanout(A, B, ptrs, N)  # noqa: E731
+    else:
+        launch = lambda: gk.gemm_tn_test(A, B, C)  # noqa: E731
     try:
         for _ in range(warm):
-            gk.gemm_tn_test(A, B, C)
+            launch()
         gk.set_trace_buffer(trace)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        gk.gemm_tn_test(A, B, C)
+        launch()
         end.record()
         torch.cuda.synchronize()
     finally:
@@ -71,6 +80,8 @@ def report(M, N, K, config, flags):
     loop = lead[:, MMA_END] - loop_start
     clock = ((t[:, EXIT] - t[:, ENTRY]) / (t[:, T1_NS] - t[:, T0_NS])).mean()
     name = {0: "normal", 1: "no loads", 2: "no stores", 4: "no MMA", 3: "no loads, no stores"}.get(flags, str(flags))
+    if FANOUT:
+        name += f", {FANOUT} outputs"
     print(f"[{text}] {name}: {ms * 1e3:.1f} us, {2.0 * M * N * K / ms / 1e9:.0f} TFLOP/s-equivalent, SM clock {clock:.3f} GHz")
     print(f"    CTAs {len(t)}, tiles per leader {lead[:, TILES].min():.0f}..{lead[:, TILES].max():.0f}; "
           f"set-up {np.mean(t[:, SETUP] - t[:, ENTRY]):.0f} cycles; first operand stage {np.mean(lead[:, MMA_FIRST] - lead[:, ENTRY]):.0f} cycles after entry")
@@ -102,7 +113,11 @@ def main():
     ap.add_argument("--configs", default="1")
     ap.add_argument("--experiments", action="store_true")
     ap.add_argument("--max-ctas", type=int, default=0, help="cap the grid (0 = all SMs): per-SM limits without power capping")
+    ap.add_argument("--fanout", type=int, default=0,
+                    help="trace gemm_tn_fanout with this many outputs in local memory (pair-tile configurations 0 and 1)")
     args = ap.parse_args()
+    global FANOUT
+    FANOUT = args.fanout
     gk.set_option("max_ctas", args.max_ctas)
     for config in [int(c) for c in args.configs.split(",")]:
         for flags in ([0, 1, 4] if args.experiments else [0]):
