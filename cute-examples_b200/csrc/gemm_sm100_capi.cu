@@ -127,7 +127,7 @@ struct EnvOverrides {
   }
   EnvOverrides() {
     read("GEMM_SM100_TILE_CONFIG", g_opt_tile_config, -1, kNumConfigs - 1);
-    read("GEMM_SM100_SPLIT_K", g_opt_split_k, -1, 8);
+    read("GEMM_SM100_SPLIT_K", g_opt_split_k, -1, 16);
     read("GEMM_SM100_GROUP_M", g_opt_group_m, 0, 4096);
     read("GEMM_SM100_MAX_CTAS", g_opt_max_ctas, 0, 1 << 20);
     read("GEMM_SM100_TIMEOUT_MS", g_opt_timeout_ms, 1, 60000);
@@ -309,6 +309,8 @@ constexpr int kSplitKConfig = 2;                      // K-split configuration o
 constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2; }
 // Configurations whose K-split kernel also has the even split (single-width tiles).
 constexpr bool has_even_split(int config) { return config == 0 || config == 2; }
+// Largest even split: a tile has 16 blocks of 32 rows x 64 columns to share out among its contributors.
+constexpr int kMaxEvenSplit = 16;
 // Configurations with a store-to-every-output kernel (the pair tiles of the multi-GPU path).
 constexpr bool has_fanout(int config) { return config == 0 || config == 1; }
 // Configurations the planner may give a balanced column tiling (256-column MMAs; the others are
@@ -508,11 +510,11 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     }
     const bool can_split = allow_split && has_split_k(i) && units >= 2;
     // Even split: every tile cut into s equal K ranges, the reduction spread over the contributors.
-    // Forced with split_k = s (2..8); automatic when it beats whole tiles and the contiguous ranges.
+    // Forced with split_k = s (2..16); automatic when it beats whole tiles and the contiguous ranges.
     int even_s = 0;
     double even_cost = 1e300;
     if (allow_split && has_even_split(i) && g_opt_split_k != 0 && g_opt_split_k != 1) {
-      for (int f = 2; f <= 8; ++f) {
+      for (int f = 2; f <= kMaxEvenSplit; ++f) {
         if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
         if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
         const double c_f = static_cast<double>(ceil_div(tiles * f, slots)) *
@@ -1153,7 +1155,7 @@ int gemm_sm100_set_option(const char* name, long value) {
     return GEMM_SM100_OK;
   }
   if (std::strcmp(name, "split_k") == 0) {
-    if (value < -1 || value > 8) return GEMM_SM100_ERR_BAD_OPTION;
+    if (value < -1 || value > kMaxEvenSplit) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_split_k = value;
     return GEMM_SM100_OK;
   }

@@ -975,46 +975,61 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
         if constexpr (Cfg::kHalves == 1) {
           if (ok && even) {
             // Every contributor of the tile has arrived once all their epilogue warps have: then this
-            // one reduces and stores its share, the 32-row x 64-column blocks b with b % factor == part
-            // (dealt round-robin to its warps), adding the partial tiles in range order.  Plain
-            // 16-byte stores from registers: a lane owns 128 contiguous bytes of one row of C.
+            // one reduces and stores its share, the 32-row x 64-column blocks b with b % factor == part,
+            // adding the partial tiles in range order.  Plain 16-byte stores from registers.
             ok = wait_counter(p.sk_flags + (size_t)seg.tile * G + cta_rank, Cfg::kEpiWarps * sk_factor, ctx,
                               kStatusTimeoutPartial);
             if (!ok) break;
             constexpr int kBlocks = 4 * kChunks;                   // 4 row quarters x 64-column chunks
-            int dealt = 0;
+            // Every warp works on every block of this contributor's share, each on its own 16 / kEpiWarps
+            // pieces (of 4 columns) of the block's 64 columns, with the loads of up to eight
+            // contributors in flight at once: the reduction is a chain of L2 round trips, and dealing
+            // whole blocks to single warps that read one contributor at a time made it eight times
+            // as long.
+            constexpr int kPieces = 16 / Cfg::kEpiWarps;
+            constexpr int kInFlight = 8;
 #pragma unroll 1
-            for (int b = seg.part; b < kBlocks; b += sk_factor, ++dealt) {
-              if (dealt % Cfg::kEpiWarps != e) continue;
+            for (int b = seg.part; b < kBlocks; b += sk_factor) {
               const int bq = b & 3, bc = b >> 2;                  // row quarter, chunk of the tile
               const int row = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + bq * 32 + (int)lane;
-              const int colc = n_tile * Cfg::kBlockN + bc * Cfg::kEpiCols;
+              const int colc = n_tile * Cfg::kBlockN + bc * Cfg::kEpiCols + e * kPieces * 4;   // this warp's columns
               if (row >= p.M || colc >= p.N || (kDebug && (dbg & kDebugSkipStores))) continue;
               uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)row * p.ldc + colc;
-              // the whole 64-column chunk of one contributor at a time: sixteen loads in flight per lane
-              float4 acc[16];
+              const size_t piece_off = (size_t)(bc * 16 + e * kPieces) * sk_rows + bq * 32 + lane;
+              float4 acc[kPieces];
 #pragma unroll 1
-              for (int i = 0; i < sk_factor; ++i) {
-                const float4* src = reinterpret_cast<const float4*>(
-                                        p.sk_partials + ((size_t)(seg.tile * sk_factor + i) * G + cta_rank) * partial_floats) +
-                                    (size_t)(bc * 16) * sk_rows + bq * 32 + lane;
-                float4 t[16];
+              for (int i0 = 0; i0 < sk_factor; i0 += kInFlight) {
+                float4 t[kInFlight][kPieces];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) t[j] = __ldcg(src + (size_t)j * sk_rows);
+                for (int ii = 0; ii < kInFlight; ++ii) {
+                  if (i0 + ii < sk_factor) {
+                    const float4* src = reinterpret_cast<const float4*>(
+                                            p.sk_partials +
+                                            ((size_t)(seg.tile * sk_factor + i0 + ii) * G + cta_rank) * partial_floats) +
+                                        piece_off;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  if (i == 0) {
-                    acc[j] = t[j];
-                  } else {
-                    acc[j].x += t[j].x;
-                    acc[j].y += t[j].y;
-                    acc[j].z += t[j].z;
-                    acc[j].w += t[j].w;
+                    for (int j = 0; j < kPieces; ++j) t[ii][j] = __ldcg(src + (size_t)j * sk_rows);
+                  }
+                }
+#pragma unroll
+                for (int ii = 0; ii < kInFlight; ++ii) {           // added in range order: the result is
+                  if (i0 + ii < sk_factor) {                       // independent of who arrived when
+#pragma unroll
+                    for (int j = 0; j < kPieces; ++j) {
+                      if (i0 + ii == 0) {
+                        acc[j] = t[ii][j];
+                      } else {
+                        acc[j].x += t[ii][j].x;
+                        acc[j].y += t[ii][j].y;
+                        acc[j].z += t[ii][j].z;
+                        acc[j].w += t[ii][j].w;
+                      }
+                    }
                   }
                 }
               }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {                       // 8 columns = 16 bytes of C per step
+              for (int j = 0; j < kPieces / 2; ++j) {             // 8 columns = 16 bytes of C per step
                 const int col = colc + j * 8;
                 const uint32_t w0 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].x), __float_as_uint(acc[2 * j].y));
                 const uint32_t w1 = pack2<Cfg::kIsBf16>(__float_as_uint(acc[2 * j].z), __float_as_uint(acc[2 * j].w));

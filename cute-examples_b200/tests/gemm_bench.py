@@ -111,7 +111,9 @@ KSPLIT_SHAPES = ("512x4096x4096,1024x4096x4096,256x8192x8192,256x512x65536,512x5
                  "2048x1024x4096,512x1024x65536")
 KSPLIT_VARIANTS = ("c0:tile_config=0,split_k=0;c3:tile_config=3,split_k=0;c2s:tile_config=2,split_k=1;"
                    "c0e2:tile_config=0,split_k=2;c0e4:tile_config=0,split_k=4;c0e8:tile_config=0,split_k=8;"
-                   "c2e2:tile_config=2,split_k=2;c2e4:tile_config=2,split_k=4;c2e8:tile_config=2,split_k=8;auto;mm")
+                   "c0e16:tile_config=0,split_k=16;"
+                   "c2e2:tile_config=2,split_k=2;c2e4:tile_config=2,split_k=4;c2e8:tile_config=2,split_k=8;"
+                   "c2e16:tile_config=2,split_k=16;auto;mm")
 
 
 def parse_variants(text):

@@ -164,7 +164,7 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  *   "timeout_ms"   bound of each device-side wait, 1..60000, default 2000.
  *   "max_ctas"     0 = all SMs (default); otherwise caps the persistent grid.
  *   "split_k"      -1 = automatic (default); 0 = never; 1 = contiguous K ranges, one per CTA or
- *                  pair, whenever the chosen configuration has a K-split variant; 2..8 = every
+ *                  pair, whenever the chosen configuration has a K-split variant; 2..16 = every
  *                  tile cut into that many equal K ranges with the reduction spread over the
  *                  contributors (256 x 256 and 128 x 256 tiles).
  *   "balance"      1 = the planner may give a tile row a number of tiles that fills the SMs evenly,

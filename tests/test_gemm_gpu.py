@@ -367,6 +367,27 @@ def test_even_split_matches_oracle(capi, shape, factor, config):
 
 
 @pytest.mark.parametrize("config", [0, 2])
+@pytest.mark.parametrize("factor", [5, 8, 12, 16])
+def test_even_split_many_ranges(capi, config, factor):
+    """Up to 16 K ranges per tile (a tile has 16 blocks to share out; with 12 ranges some contributors
+    reduce two blocks and some one, with 16 one each): tolerance against the oracle, exact on
+    integers, same bits on every run."""
+    M, N, K = 300, 520, 64 * 8 * factor + 64
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"split_k", factor)
+    assert "K ranges" in plan_text(capi, M, N, K)
+    A, B = oracle.make_inputs(M, N, K, 240 + factor)
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    assert torch.equal(C.view(torch.int16), run_capi(capi, A, B).view(torch.int16))
+    At, Bt = oracle.make_ternary_inputs(M, N, 256, 241)
+    At = torch.cat([At, torch.zeros(M, K - 256, dtype=At.dtype)], dim=1)
+    Bt = torch.cat([Bt, torch.zeros(N, K - 256, dtype=Bt.dtype)], dim=1)
+    Ct = run_capi(capi, At, Bt)
+    assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+@pytest.mark.parametrize("config", [0, 2])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_even_split_exact_on_integers(capi, dtype, config):
     M, N, K = 384, 1288, 2048           # N % 8 == 0 but not a multiple of 64: ragged last chunk
