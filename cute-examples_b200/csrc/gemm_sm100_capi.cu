@@ -18,6 +18,8 @@
 #include <atomic>
 #include <mutex>
 #include <utility>
+#include <vector>
+#include <cstdint>
 
 #include "../../include/gemm_sm100.h"
 #include "gemm_tn_sm100.cuh"
@@ -97,6 +99,36 @@ std::atomic<long> g_opt_balance{1};    // 1: the planner may choose a balanced c
 std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
 // Bumped by every gemm_sm100_set_option: cached plans of an older generation are stale.
 std::atomic<unsigned> g_opt_generation{1};
+
+// Workspaces registered with gemm_sm100_workspace_register: the library zero-fills the start once
+// and from then on knows how long a prefix the launches queued so far leave zeroed.
+struct KeptWorkspace {
+  void* ptr;
+  size_t clean_bytes;   // this prefix is zero once the work queued so far has run
+};
+constexpr size_t kKeptWorkspaceZeroBytes = 4096;   // more than any plan's counter area
+std::mutex g_kept_mutex;
+std::vector<KeptWorkspace> g_kept_workspaces;
+
+// Whether the counter area (the first `flag_bytes` of `workspace`) has to be zero-filled before a
+// K-split launch.  `self_resetting`: the launch leaves its counters at zero (the even split does,
+// the contiguous one does not).  The partial tiles follow the counters, so after the launch nothing
+// beyond `flag_bytes` is known to be zero.
+bool kept_workspace_needs_zeroing(void* workspace, size_t flag_bytes, bool self_resetting) {
+  std::lock_guard<std::mutex> lock(g_kept_mutex);
+  for (KeptWorkspace& w : g_kept_workspaces) {
+    if (w.ptr != workspace) continue;
+    const bool zero_already = flag_bytes <= w.clean_bytes;
+    w.clean_bytes = self_resetting ? flag_bytes : 0;
+    return !zero_already;
+  }
+  return true;
+}
+
+void kept_workspaces_mark_dirty() {
+  std::lock_guard<std::mutex> lock(g_kept_mutex);
+  for (KeptWorkspace& w : g_kept_workspaces) w.clean_bytes = 0;
+}
 // Trace buffer (gemm_sm100_set_trace_buffer): pointer, size and the device that owns the memory,
 // kept together under g_mutex so that a launch reads a consistent triple.  Launches on any other
 // device ignore the buffer (its address means nothing there).
@@ -762,8 +794,12 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
     tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
     tp.sk_rows = plan.partial_rows;
     tp.sk_factor = plan.split_factor;
-    e = cudaMemsetAsync(tp.sk_flags, 0, plan.flag_bytes, stream);
-    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    // The even split's counters return to zero by themselves; a registered workspace that was left
+    // by such a launch needs no memset (and the kernel can then overlap the previous one's tail).
+    if (kept_workspace_needs_zeroing(workspace, plan.flag_bytes, plan.split_factor > 1)) {
+      e = cudaMemsetAsync(tp.sk_flags, 0, plan.flag_bytes, stream);
+      if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    }
   }
 
   CUtensorMap map_a, map_b, map_c;
@@ -1123,11 +1159,39 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out) {
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   if (status_out) *status_out = word;
   if (word != 0) {
+    kept_workspaces_mark_dirty();   // a kernel that gave up may have left arrival counters behind
     e = cudaMemset(st->status_ptr, 0, sizeof(word));
     if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
     return GEMM_SM100_ERR_DEVICE_TIMEOUT;
   }
   return GEMM_SM100_OK;
+}
+
+int gemm_sm100_workspace_register(void* workspace, size_t workspace_bytes, void* stream, int* cuda_error_out) {
+  if (cuda_error_out) *cuda_error_out = 0;
+  if (!workspace) return GEMM_SM100_ERR_NULL_POINTER;
+  if (workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return GEMM_SM100_ERR_WORKSPACE;
+  const size_t bytes = workspace_bytes < kKeptWorkspaceZeroBytes ? workspace_bytes / 256 * 256 : kKeptWorkspaceZeroBytes;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+  std::lock_guard<std::mutex> lock(g_kept_mutex);
+  for (KeptWorkspace& w : g_kept_workspaces)
+    if (w.ptr == workspace) {
+      w.clean_bytes = bytes;
+      return GEMM_SM100_OK;
+    }
+  g_kept_workspaces.push_back({workspace, bytes});
+  return GEMM_SM100_OK;
+}
+
+int gemm_sm100_workspace_unregister(void* workspace) {
+  std::lock_guard<std::mutex> lock(g_kept_mutex);
+  for (size_t i = 0; i < g_kept_workspaces.size(); ++i)
+    if (g_kept_workspaces[i].ptr == workspace) {
+      g_kept_workspaces.erase(g_kept_workspaces.begin() + static_cast<long>(i));
+      return GEMM_SM100_OK;
+    }
+  return GEMM_SM100_ERR_WORKSPACE;
 }
 
 int gemm_sm100_set_option(const char* name, long value) {

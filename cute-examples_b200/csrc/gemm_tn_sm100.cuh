@@ -296,14 +296,16 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
   return wait_slow(bar, parity, ctx, code);
 }
 
-// Bounded wait (whole warp) until a global arrival counter reaches `want`.
+// Bounded wait (whole warp) until a global arrival counter reaches `want`.  Arrivals are counted in
+// the low 16 bits; the high bits count the warps that are done with the partial tiles (see the even
+// K-split below).
 __device__ __noinline__ bool wait_counter(const unsigned int* counter, unsigned int want, const WaitCtx& ctx,
                                           uint32_t code) {
   const volatile unsigned int* c = counter;
   uint64_t t0 = 0;
 #pragma unroll 1
   for (unsigned int spin = 0;; ++spin) {
-    if (__all_sync(0xffffffffu, *c >= want)) {
+    if (__all_sync(0xffffffffu, (*c & 0xffffu) >= want)) {
       __threadfence();   // acquire: the partial sums written before the arrivals are visible now
       return true;
     }
@@ -1044,6 +1046,15 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
                     if (col + t2 < p.N) crow[j * 8 + t2] = (uint16_t)(w[t2 >> 1] >> (16 * (t2 & 1)));
                 }
               }
+            }
+            // Done with the tile's partial sums.  The last of the tile's warps to say so puts the
+            // counter back to zero, so a workspace that starts out zeroed is zeroed again when the
+            // launch completes and the next launch needs no memset in front of it.
+            __syncwarp();
+            if (lane == 0) {
+              unsigned int* counter = p.sk_flags + (size_t)seg.tile * G + cta_rank;
+              const unsigned int before = atomicAdd(counter, 0x10000u);
+              if ((before >> 16) == (unsigned int)(Cfg::kEpiWarps * sk_factor) - 1u) atomicExch(counter, 0u);
             }
           }
         }

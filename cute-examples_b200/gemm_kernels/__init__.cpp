@@ -47,7 +47,12 @@ void* kept_workspace(const c10::Device& device, cudaStream_t stream, size_t byte
   if (!t.defined() || static_cast<size_t>(t.numel()) < bytes) {
     // the old buffer (if any) goes back to the allocator, which keeps it alive for the work
     // already queued on the stream it was allocated on
+    if (t.defined()) gemm_sm100_workspace_unregister(t.data_ptr());
     t = torch::empty({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(device));
+    // kept by the library from here on: zero-filled once, no memset in front of the even K-split
+    int cuda_error = 0;
+    const int rc = gemm_sm100_workspace_register(t.data_ptr(), bytes, static_cast<void*>(stream), &cuda_error);
+    TORCH_CHECK(rc == GEMM_SM100_OK, "gemm_sm100_workspace_register: ", gemm_sm100_error_string(rc), " cuda=", cuda_error);
   }
   return t.data_ptr();
 }

@@ -146,6 +146,23 @@ size_t gemm_sm100_static_scratch_capacity(void);
  * kernel needs no workspace (gemm_test.cu:70-85). */
 size_t gemm_sm100_workspace_bytes(int M, int N, int K, int dtype);
 
+/* Optional: hands a workspace to the library for keeping.  The first 4 KiB (the arrival counters of
+ * any plan) are zero-filled once, on `cuda_stream`; from then on a K-split launch that is given this
+ * pointer skips the memset in front of the kernel whenever the previous launch on it left the
+ * counters at zero, which the even K-split does by itself.  Without the memset node the kernel is a
+ * programmatic dependent of the previous one like the unsplit kernels are.  The caller promises
+ * that nothing else writes the workspace while it is registered, that launches using it are ordered
+ * one after another (one stream, or events), and calls gemm_sm100_workspace_unregister before
+ * freeing it.  After gemm_sm100_device_status has reported a time-out every registered workspace is
+ * zero-filled again before its next use.  `workspace`: 256-byte aligned, at least 256 bytes.
+ * Returns GEMM_SM100_OK, GEMM_SM100_ERR_WORKSPACE, GEMM_SM100_ERR_NULL_POINTER or
+ * GEMM_SM100_ERR_CUDA.  No reference counterpart (the reference needs no workspace). */
+int gemm_sm100_workspace_register(void* workspace, size_t workspace_bytes, void* cuda_stream,
+                                  int* cuda_error_out);
+
+/* Forgets a registered workspace (GEMM_SM100_ERR_WORKSPACE if it was not registered). */
+int gemm_sm100_workspace_unregister(void* workspace);
+
 /* Number of SMs of the current device (the persistent grid is sized from it; the
  * reference hard-codes 132, gemm_test.cu:72).  Returns a negative value on error. */
 int gemm_sm100_num_sms(void);

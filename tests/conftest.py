@@ -61,6 +61,10 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_static_scratch_capacity.restype = Z
     lib.gemm_sm100_workspace_bytes.argtypes = [I, I, I, I]
     lib.gemm_sm100_workspace_bytes.restype = Z
+    lib.gemm_sm100_workspace_register.argtypes = [P, Z, P, ctypes.POINTER(I)]
+    lib.gemm_sm100_workspace_register.restype = I
+    lib.gemm_sm100_workspace_unregister.argtypes = [P]
+    lib.gemm_sm100_workspace_unregister.restype = I
     lib.gemm_sm100_num_sms.argtypes = []
     lib.gemm_sm100_num_sms.restype = I
     lib.gemm_sm100_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(I)]

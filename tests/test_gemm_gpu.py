@@ -418,6 +418,46 @@ def test_even_split_ragged_n_inside_wider_buffer(capi):
     assert torch.equal(got[:, 8 + N:].view(torch.int16), wide0[:, 8 + N:].view(torch.int16))
 
 
+def test_registered_workspace_needs_no_memset(capi):
+    """A workspace handed to the library for keeping: the even K-split leaves its arrival counters at
+    zero, so launches follow one another on it without a memset (same bits as with a fresh, unregistered
+    workspace every time); a contiguous split in between leaves counters behind and the next launch
+    zero-fills again."""
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    ws.fill_(0xAB)
+    err = ctypes.c_int(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert capi.gemm_sm100_workspace_register(None, 4096, stream, ctypes.byref(err)) == 1
+    assert capi.gemm_sm100_workspace_register(ws.data_ptr() + 16, 4096, stream, ctypes.byref(err)) == 7
+    assert capi.gemm_sm100_workspace_unregister(ws.data_ptr()) == 7          # not registered yet
+    assert capi.gemm_sm100_workspace_register(ws.data_ptr(), ws.numel(), stream, ctypes.byref(err)) == 0
+    try:
+        # (shape, tile configuration, split_k option); twice through, so every kind follows every other
+        cases = [((300, 520, 2048 + 64), 0, 4), ((256, 512, 64 * 8 * 16), 2, 16), ((100, 1104, 4096), 2, 1),
+                 ((384, 264, 4096), 0, 8), ((64, 2048, 8192), 1, 1), ((130, 304, 2048), 2, 2)]
+        for (M, N, K), config, split in cases + cases:
+            capi.gemm_sm100_set_option(b"tile_config", config)
+            capi.gemm_sm100_set_option(b"split_k", split)
+            assert "K ranges" in plan_text(capi, M, N, K) or split == 1
+            A, B = oracle.make_inputs(M, N, K, 250 + split)
+            want = run_capi(capi, A, B)                                       # its own workspace, memset
+            Ad, Bd = A.cuda(), B.cuda()
+            C = torch.full((M, N), float("nan"), dtype=A.dtype, device="cuda")
+            need = capi.gemm_sm100_workspace_bytes(M, N, K, 0)
+            assert 0 < need <= ws.numel()
+            rc = capi.gemm_sm100_tn(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0,
+                                    ws.data_ptr(), ws.numel(), stream, ctypes.byref(err))
+            assert rc == 0
+            assert capi_status(capi) == (0, 0)
+            assert torch.equal(C.cpu().view(torch.int16), want.view(torch.int16)), (M, N, K, config, split)
+            if split > 1:
+                # the counters (one per tile and CTA of the pair, at the start) are back at zero
+                assert int(ws[:64].to(torch.int32).sum().item()) == 0, "counters did not return to zero"
+    finally:
+        assert capi.gemm_sm100_workspace_unregister(ws.data_ptr()) == 0
+    assert capi.gemm_sm100_workspace_unregister(ws.data_ptr()) == 7
+
+
 def test_split_k_rejects_missing_workspace(capi):
     M, N, K = 128, 2048, 4096
     capi.gemm_sm100_set_option(b"tile_config", 2)
