@@ -610,18 +610,21 @@ def run_multi(args):
     mm_step = lambda: torch.mm(A, B_shard.T, out=C_mm)  # noqa: E731
     local_step()
     mm_step()
-    # Blocks of `steps` back-to-back launches, ours and cuBLAS in turn, twice: the same regime (power-
-    # capped, no idle gaps) as the fused step above.  Launches timed one by one with a synchronise in
-    # between would run cooler and faster and make the exchange look expensive.
-    ours_ms, mm_ms = [], []
+    # Blocks of `steps` back-to-back launches: the fused step, this kernel alone and cuBLAS in turn,
+    # twice, after a run-in of the same work that is long enough (several hundred ms) for the GPUs to
+    # settle at the power cap the parity check's idle seconds lifted.  Launches timed one by one, or
+    # short blocks after an idle gap, run in the boost state and make the exchange look expensive.
+    for _ in range(3 * max(args.steps, 10)):
+        local_step()
+    ours_ms, mm_ms, fused_ms = [], [], []
     for _ in range(2):
-        for fn, acc in ((local_step, ours_ms), (mm_step, mm_ms)):
+        for fn, acc in ((step, fused_ms), (local_step, ours_ms), (mm_step, mm_ms)):
             acc.append(time_steps(fn, args.steps, torch.cuda.synchronize, barrier) / 2)
     gk.device_status()
     local_total, mm_total = sum(ours_ms), sum(mm_ms)
-    t = torch.tensor([local_total, mm_total], dtype=torch.float64, device=device)
+    t = torch.tensor([local_total, mm_total, sum(fused_ms)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    local_ms, cublas_ms = t[0].item() / args.steps, t[1].item() / args.steps
+    local_ms, cublas_ms, fused_alt_ms = (t[i].item() / args.steps for i in range(3))
     local_ms_per_rank = per_rank(local_total, args.steps)
     cublas_ms_per_rank = per_rank(mm_total, args.steps)
     slab_max_diff = float((C_slab[rows_d].float() - C_mm[rows_d].float()).abs().max().item())
@@ -664,17 +667,19 @@ def run_multi(args):
             "details": {"exchange": how, "nsplit_mode": mode, "per_gpu_tflops": round(per_gpu, 2),
                         "local_gemm_ms_per_step": round(local_ms, 4),
                         "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange: blocks of "
-                                           "`steps` back-to-back launches, in turn with blocks of cuBLAS (torch.mm) "
-                                           "on the same slab, two blocks each",
+                                           "`steps` back-to-back launches, in turn with blocks of the whole step and "
+                                           "of cuBLAS (torch.mm) on the same slab, two blocks each, after a run-in",
                         "local_gemm_ms_per_rank": local_ms_per_rank,
                         "cublas_slab_ms_per_step": round(cublas_ms, 4),
                         "cublas_slab_ms_per_rank": cublas_ms_per_rank,
                         "ours_over_cublas_time": round(local_ms / cublas_ms, 4),
                         "slab_max_abs_diff_vs_cublas": slab_max_diff,
-                        "exchange_overhead": round(ms / local_ms - 1.0, 4),
-                        "exchange_overhead_note": "fused step time / slowest rank's plain slab GEMM - 1; the GPUs of a "
-                                                  "box differ under the power cap and a step that ends in a cross-GPU "
-                                                  "barrier runs at the slowest one's pace"},
+                        "step_ms_in_alternation": round(fused_alt_ms, 4),
+                        "exchange_overhead": round(fused_alt_ms / local_ms - 1.0, 4),
+                        "exchange_overhead_note": "step time / slowest rank's plain slab GEMM - 1, both from the blocks "
+                                                  "timed in alternation after the run-in (same power state); the GPUs "
+                                                  "of a box differ under the power cap and a step that ends in a "
+                                                  "cross-GPU barrier runs at the slowest one's pace"},
             "e2e": {"value": round(gemm_flops(M, N, K) / e2e_ms / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,
                     "note": "bytes summed over ranks: rank g uploads 1/G of A (replicated over NVLink by an "

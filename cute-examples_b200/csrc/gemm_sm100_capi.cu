@@ -92,6 +92,7 @@ std::atomic<long> g_opt_max_ctas{0};
 std::atomic<long> g_opt_debug_flags{0};
 std::atomic<long> g_opt_group_m{0};
 std::atomic<long> g_opt_k_rotate{-1};   // 0 never, 1 always, -1 (default) when there is a single tile row: 3 % on the few-row shapes, 2 = serpentine
+std::atomic<long> g_opt_sk_cluster{-1};  // cluster K-split (partial sums through distributed shared memory): -1 planner, 0 never, 1 always where an even split of 2, 4 or 8 is made
 std::atomic<long> g_opt_pdl{1};        // 1: launch with programmatic stream serialization (overlap with the previous kernel's tail)
 std::atomic<long> g_opt_early_prefetch{1};   // with pdl: L2 prefetch of the first stages before waiting for the previous kernel
 std::atomic<long> g_opt_tiles_n{0};    // > 0: force this many tiles per tile row (tests), when the configuration allows the widths
@@ -355,6 +356,19 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // tiles written, the wait for the other contributors, one tile's worth of partial data read back
 // and stored; little of it overlaps the next unit's main loop).
 constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+// The same for the cluster K-split (2, 4 or 8 ranges per tile, the contributors of a tile in one
+// cluster, partial sums exchanged through distributed shared memory: no workspace, no counters, no
+// trip through L2).
+constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {20.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+
+// Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
+// one GPC, and a GPC of this generation has about 18 SMs.
+inline long resident_clusters(int sm_count, int cluster_ctas) {
+  const int gpcs = sm_count >= 36 ? sm_count / 18 : 1;
+  const int per_gpc = sm_count / gpcs;
+  const long n = static_cast<long>(gpcs) * (per_gpc / cluster_ctas);
+  return n > 0 ? n : 1;
+}
 
 struct Plan {
   int config = 0;
@@ -366,6 +380,7 @@ struct Plan {
   size_t partial_bytes = 0;  // K-split: one fp32 partial tile per CTA
   int partial_rows = 128;    // K-split: rows kept per partial tile
   int split_factor = 0;      // K-split: > 1 = every tile cut into this many equal K ranges
+  bool cluster = false;      // even split whose contributors form a cluster and exchange partial sums in shared memory
 };
 
 inline int grid_cap(const ConfigInfo& c, int sm_count) {
@@ -544,16 +559,33 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     // Even split: every tile cut into s equal K ranges, the reduction spread over the contributors.
     // Forced with split_k = s (2..16); automatic when it beats whole tiles and the contiguous ranges.
     int even_s = 0;
+    bool even_cluster = false;
     double even_cost = 1e300;
     if (allow_split && has_even_split(i) && g_opt_split_k != 0 && g_opt_split_k != 1) {
+      const long sk_cluster = g_opt_sk_cluster.load();
       for (int f = 2; f <= kMaxEvenSplit; ++f) {
         if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
         if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
-        const double c_f = static_cast<double>(ceil_div(tiles * f, slots)) *
-                           (static_cast<double>(k_blocks) / f + boundary + kEvenSplitFixupKBlocks[i]) * block_n / rate;
-        if (c_f < even_cost) {
-          even_cost = c_f;
-          even_s = f;
+        if (sk_cluster != 1 || (f != 2 && f != 4 && f != 8) || f * c.cta_group > 8) {
+          const double c_f = static_cast<double>(ceil_div(tiles * f, slots)) *
+                             (static_cast<double>(k_blocks) / f + boundary + kEvenSplitFixupKBlocks[i]) * block_n / rate;
+          if (c_f < even_cost) {
+            even_cost = c_f;
+            even_s = f;
+            even_cluster = false;
+          }
+        }
+        if (sk_cluster != 0 && (f == 2 || f == 4 || f == 8) && f * c.cta_group <= 8 &&   // portable cluster sizes
+            tiles * f * c.cta_group <= 65535) {
+          // one unit per CTA (pair), as many waves of clusters as that takes
+          const long held = resident_clusters(sm_count, f * c.cta_group);
+          const double c_f = static_cast<double>(ceil_div(tiles, held)) *
+                             (static_cast<double>(k_blocks) / f + boundary + kClusterSplitFixupKBlocks[i]) * block_n / rate;
+          if (c_f < even_cost) {
+            even_cost = c_f;
+            even_s = f;
+            even_cluster = true;
+          }
         }
       }
     }
@@ -568,6 +600,11 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
       cand.partial_rows = M < 128 ? static_cast<int>((M + 31) / 32 * 32) : 128;
       cand.flag_bytes = (static_cast<size_t>(tiles) * c.cta_group * sizeof(unsigned int) + 255) / 256 * 256;
       cand.partial_bytes = static_cast<size_t>(even_units) * c.cta_group * cand.partial_rows * block_n * sizeof(float);
+      if (even_cluster) {
+        cand.cluster = true;
+        cand.ctas = static_cast<int>(even_units * c.cta_group);
+        cand.flag_bytes = cand.partial_bytes = 0;            // nothing goes through global memory
+      }
     } else if (can_split && (g_opt_split_k == 1 || auto_split)) {
       cost = split_cost;
       cand.tiles_n = cand.bal_q = cand.bal_rem = 0;
@@ -640,6 +677,7 @@ TileParams base_tile_params(const Problem& p, const DeviceState& st) {
   tp.sk_partials = nullptr;
   tp.sk_rows = 128;
   tp.sk_factor = 0;
+  tp.sk_cluster = 0;
   tp.k_rotate = 0;
   tp.alpha = p.alpha;
   tp.beta = p.beta;
@@ -660,7 +698,7 @@ int k_order_for(const Problem& p, bool split_k) {
 
 // Cluster launch of `kernel` on `ctas` CTAs of Cfg::kThreads threads.
 template <class Cfg, class Kernel, class... Args>
-cudaError_t launch_kernel(Kernel kernel, long ctas, cudaStream_t stream, const Args&... args) {
+cudaError_t launch_kernel(Kernel kernel, long ctas, int cluster_ctas, cudaStream_t stream, const Args&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(ctas));
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -668,9 +706,9 @@ cudaError_t launch_kernel(Kernel kernel, long ctas, cudaStream_t stream, const A
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   unsigned n = 0;
-  if (Cfg::kCtaGroup == 2) {                           // single-CTA tiles are launched without a cluster
+  if (cluster_ctas > 1) {                              // single-CTA tiles are launched without a cluster
     attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = Cfg::kCtaGroup;
+    attrs[n].val.clusterDim.x = static_cast<unsigned>(cluster_ctas);
     attrs[n].val.clusterDim.y = 1;
     attrs[n].val.clusterDim.z = 1;
     ++n;
@@ -789,7 +827,10 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   }
   tp.debug_flags = static_cast<unsigned int>(g_opt_debug_flags.load());
   tp.k_rotate = k_order_for(p, plan.split_k);
-  if (plan.split_k) {
+  if (plan.split_k && plan.cluster) {
+    tp.sk_factor = plan.split_factor;
+    tp.sk_cluster = 1;
+  } else if (plan.split_k) {
     tp.sk_flags = static_cast<unsigned int*>(workspace);
     tp.sk_partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.flag_bytes);
     tp.sk_rows = plan.partial_rows;
@@ -811,7 +852,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   if (rc) return rc;
 
   long ctas = plan.ctas;
-  if (ctas > st.max_ctas[kCfgIndex][dt]) {
+  if (ctas > st.max_ctas[kCfgIndex][dt] && !plan.cluster) {   // (the cluster split runs in as many waves as it takes)
     // Fewer co-resident CTAs than SMs (never seen on B200).  The K-split schedule needs the
     // grid it was planned for, because the workspace is indexed by CTA.
     if (plan.split_k) return set_cuda_error(cuda_error_out, cudaErrorLaunchOutOfResources);
@@ -820,7 +861,8 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   if (trace.ptr && trace.bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
     tp.trace = trace.ptr;
 
-  e = launch_kernel<Cfg>(kernel, ctas, stream, map_a, map_b, map_c, tp);
+  e = launch_kernel<Cfg>(kernel, ctas, plan.cluster ? plan.split_factor * Cfg::kCtaGroup : Cfg::kCtaGroup, stream, map_a, map_b,
+                          map_c, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -857,7 +899,7 @@ int launch_fanout(const Problem& p, void* const* outputs, int num_outputs, Devic
   if (trace.ptr && trace.bytes >= static_cast<size_t>(ctas) * kTraceWords * sizeof(unsigned long long))
     tp.trace = trace.ptr;
 
-  cudaError_t e = launch_kernel<Cfg>(kernel, ctas, stream, map_a, map_b, out, num_outputs, tp);
+  cudaError_t e = launch_kernel<Cfg>(kernel, ctas, Cfg::kCtaGroup, stream, map_a, map_b, out, num_outputs, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -884,7 +926,7 @@ int launch_nn(const Problem& p, const Plan& plan, DeviceState& st, cudaStream_t 
   if (rc) return rc;
   rc = encode_2d_cached(&map_c, p.C, p.dtype, p.M, tma_store_cols(p.N), p.ldc, 32, cuda_error_out);
   if (rc) return rc;
-  const cudaError_t e = launch_kernel<Cfg>(kernel, plan.ctas, stream, map_a, map_b, map_c, tp);
+  const cudaError_t e = launch_kernel<Cfg>(kernel, plan.ctas, Cfg::kCtaGroup, stream, map_a, map_b, map_c, tp);
   if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   return GEMM_SM100_OK;
 }
@@ -953,7 +995,7 @@ int gemm_sm100_tn(const void* A, const void* B, void* C, int M, int N, int K, lo
     if (rc != GEMM_SM100_OK) return rc;
   }
   Plan plan = plan_for(M, N, K, st->sm_count);
-  if (plan.split_k) {
+  if (plan.split_k && !plan.cluster) {
     if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
         workspace_bytes < plan.flag_bytes + plan.partial_bytes) {
       // A K-split the caller asked for needs its workspace; one the planner chose by itself is
@@ -1223,6 +1265,11 @@ int gemm_sm100_set_option(const char* name, long value) {
     g_opt_split_k = value;
     return GEMM_SM100_OK;
   }
+  if (std::strcmp(name, "sk_cluster") == 0) {
+    if (value < -1 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
+    g_opt_sk_cluster = value;
+    return GEMM_SM100_OK;
+  }
   if (std::strcmp(name, "pdl") == 0) {
     if (value < 0 || value > 1) return GEMM_SM100_ERR_BAD_OPTION;
     g_opt_pdl = value;
@@ -1302,11 +1349,12 @@ int gemm_sm100_describe_plan(int M, int N, int K, int dtype, char* buf, size_t b
                   plan.bal_start);
   else
     std::snprintf(tiling, sizeof(tiling), "uniform: %ld tiles per row of %d columns", ceil_div(N, block_n), block_n);
-  char split[64];
+  char split[96];
   if (!plan.split_k)
     std::snprintf(split, sizeof(split), "whole tiles");
   else if (plan.split_factor > 1)
-    std::snprintf(split, sizeof(split), "every tile cut into %d K ranges", plan.split_factor);
+    std::snprintf(split, sizeof(split), "every tile cut into %d K ranges%s", plan.split_factor,
+                  plan.cluster ? " (one cluster per tile)" : "");
   else
     std::snprintf(split, sizeof(split), "contiguous K ranges");
   std::snprintf(buf, buf_bytes, "config=%d tile=%dx%dx64 %s; %s; ctas=%d workspace=%zu", plan.config, 128 * c.cta_group,

@@ -91,6 +91,10 @@ struct TileParams {
   int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
   int sk_factor;                   // <= 1: contiguous ranges; > 1: every tile cut into this many equal K ranges
                                    // (then one partial tile per unit and CTA of the pair, one counter per tile and CTA)
+  // > 0 (even split with sk_factor 2, 4 or 8, launched in clusters of sk_factor CTA (pair)s, one unit
+  // per CTA (pair)): the contributors of a tile sit in one cluster and exchange their partial sums
+  // through distributed shared memory instead of the workspace, which is then not used at all.
+  int sk_cluster;
   // Order in which a tile's K blocks are loaded (the sum does not depend on it beyond rounding):
   // 0 ascending.  1 ("rotate"): every tile starts at a different K block and wraps around, so CTAs
   // that each stream their own B tile hit different column offsets at any moment.  2
@@ -416,18 +420,25 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   const uint32_t bar_base = smem_u32(bar_mem);
   constexpr uint32_t kFullOff = 0, kEmptyOff = 8u * kStages, kTFullOff = 16u * kStages,
                      kTEmptyOff = 16u * kStages + 16u, kTmemReadyOff = 16u * kStages + 32u;
-  static_assert(8 * (2 * kStages + 5) + 8 <= Cfg::kBarrierBytes, "barrier block too small");
+  // cluster K-split: "every contributor's operand ring is idle" and "every contributor's partial sums are here"
+  constexpr uint32_t kRxReadyOff = Cfg::kBarrierBytes - 16, kRxDoneOff = Cfg::kBarrierBytes - 8;
+  static_assert(8 * (2 * kStages + 5) + 8 <= Cfg::kBarrierBytes - 16, "barrier block too small");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mem + 8 * (2 * kStages + 5));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
-  const uint32_t cta_rank = (G == 2) ? cluster_ctarank() : 0u;
+  // A pair is two CTAs of the cluster whose ranks differ in the last bit.  Clusters are pairs,
+  // except for the cluster K-split, where a cluster holds all contributors of a tile.
+  const uint32_t cluster_rank = cluster_ctarank();
+  const uint32_t cta_rank = (G == 2) ? (cluster_rank & 1u) : 0u;
+  const uint32_t pair_base = cluster_rank - cta_rank;        // cluster rank of this pair's leader
   const bool is_leader = cta_rank == 0;
+  const bool cluster_split = kSplitK && Cfg::kHalves == 1 && p.sk_cluster > 0;
 
   WaitCtx ctx;
   ctx.abort_flag = abort_flag;
-  ctx.peer_abort_addr = (G == 2) ? map_to_cta(smem_u32((const void*)abort_flag), cta_rank ^ 1u)
+  ctx.peer_abort_addr = (G == 2) ? map_to_cta(smem_u32((const void*)abort_flag), pair_base + (cta_rank ^ 1u))
                                  : smem_u32((const void*)abort_flag);
   ctx.status = p.status;
   ctx.timeout_ns = p.timeout_ns;
@@ -446,12 +457,18 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       mbar_init(bar_base + kTEmptyOff + 8u * a, Cfg::kEpiWarps * G);   // every epilogue warp of the pair arrives once
     }
     mbar_init(bar_base + kTmemReadyOff, 1);   // pair mode: the peer's TMEM allocation is done
+    if constexpr (kSplitK) {
+      // every epilogue warp of every contributor to this CTA's rows arrives once on each
+      const uint32_t arrivals = (uint32_t)(Cfg::kEpiWarps * (p.sk_cluster > 0 ? p.sk_factor : 1));
+      mbar_init(bar_base + kRxReadyOff, arrivals);
+      mbar_init(bar_base + kRxDoneOff, arrivals);
+    }
     fence_mbar_init();
   }
   // Barriers are initialised: let the producer go.  The TMEM allocation (slow for a CTA pair)
   // happens after this point, off the path of the first operand loads.
   __syncthreads();
-  if constexpr (G == 2) {
+  if (G == 2 || cluster_split) {
     cluster_arrive();
     cluster_wait();
   }
@@ -470,7 +487,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     tmem_base = *tmem_slot;
     if constexpr (G == 2) {
       // The leader's MMAs write both CTAs' TMEM: it must know the peer's allocation is done.
-      if (warp == 1 && !is_leader && lane == 0) mbar_arrive_cluster(map_to_cta(bar_base + kTmemReadyOff, 0u));
+      if (warp == 1 && !is_leader && lane == 0) mbar_arrive_cluster(map_to_cta(bar_base + kTmemReadyOff, pair_base));
     }
   }
 
@@ -523,7 +540,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       const uint64_t pol = policy_evict_normal();
       // Both CTAs of a pair complete their bytes on the LEADER's barrier: the leader's MMA
       // thread is the only consumer of the ring.
-      const uint32_t full_leader = (G == 2) ? map_to_cta(bar_base + kFullOff, 0u) : bar_base + kFullOff;
+      const uint32_t full_leader = (G == 2) ? map_to_cta(bar_base + kFullOff, pair_base) : bar_base + kFullOff;
       uint32_t phase = 0;
       WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
       Segment seg;
@@ -629,7 +646,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       // start-address step (16-byte units) of B per 16-element K step: 32 bytes along a K-major row,
       // two 8-row groups of 1024 bytes for the MN-major layout
       constexpr uint32_t kBStepK = kBIsKN ? 128u : 2u;
-      const uint32_t bar_peer = (G == 2) ? map_to_cta(bar_base, 1u) : bar_base;
+      const uint32_t bar_peer = (G == 2) ? map_to_cta(bar_base, pair_base + 1u) : bar_base;
       uint32_t phase = 0;
       WorkIter<kSplitK> work(cluster_id, num_clusters, num_tiles, k_blocks, sk_factor);
       Segment seg;
@@ -743,7 +760,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     const int cg = e >> 2;
     constexpr int kChunks = Cfg::kMmaN / Cfg::kEpiCols;      // 64-column chunks per accumulator slot
     const uint32_t stage_buf = smem_epi + (uint32_t)e * Cfg::kEpiBufs * Cfg::kEpiWarpBuf;
-    const uint32_t tempty_leader = ((G == 2) ? map_to_cta(bar_base, 0u) : bar_base) + kTEmptyOff;
+    const uint32_t tempty_leader = ((G == 2) ? map_to_cta(bar_base, pair_base) : bar_base) + kTEmptyOff;
     int iter = 0;
     uint32_t buf = 0;
     bool ok = true;
@@ -755,6 +772,13 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     const int sk_rows = kSplitK ? p.sk_rows : Cfg::kBlockM;
     const size_t partial_floats = (size_t)sk_rows * Cfg::kBlockN;
     const int my_row = q * 32 + (int)lane;                   // row of the CTA's 128 x kBlockN tile
+    // cluster K-split: a contributor's share of the tile's 16-byte pieces (kBlockN / 4 of them) is
+    // 2^rx_share_shift pieces wide
+    int rx_share_shift = 0;
+    if constexpr (kSplitK) {
+      if (cluster_split)
+        while (((Cfg::kBlockN / 4) >> rx_share_shift) > sk_factor) ++rx_share_shift;
+    }
     for (; ok && work.next(seg); ++iter) {
       int m_tile, n_tile;
       tile_coords(seg.tile, p, m_tile, n_tile);
@@ -799,11 +823,42 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
         if constexpr (kDebug)
           if (trace) stall += clock64() - te;
         tc_fence_after_sync();
+        if constexpr (kSplitK) {
+          if (cluster_split) {
+            // This CTA's accumulator is complete, so its operand ring is idle: it becomes the place
+            // where the tile's contributors leave their partial sums of this CTA's share.  Tell
+            // every contributor, and wait until all of them have said the same.
+            __syncwarp();
+            if ((int)lane < sk_factor)
+              mbar_arrive_cluster_release(map_to_cta(bar_base + kRxReadyOff, lane * G + cta_rank));
+            if (!wait_bounded(bar_base + kRxReadyOff, 0u, ctx, kStatusTimeoutPartial + 1)) {
+              ok = false;
+              break;
+            }
+            fence_acq_rel_cluster();
+          }
+        }
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + slot * Cfg::kSlotCols;
         // Everything that happens to one 32-row x 64-column chunk once it sits in registers.
         auto finish_chunk = [&](const int c, uint32_t (&v0)[32], uint32_t (&v1)[32]) {
           if constexpr (kSplitK) {
             const int piece0 = (h * kChunks + c) * 16;       // first 16-byte piece of this chunk
+            if (cluster_split) {
+              // 16-byte piece P of the tile's columns belongs to contributor P / share; it goes into
+              // that CTA's ring, laid out [sender][piece of the share][row], 16 bytes each.
+              if (row_live) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const uint32_t* v = (j < 8) ? &v0[4 * j] : &v1[4 * (j - 8)];
+                  const int piece = piece0 + j;
+                  const int owner = piece >> rx_share_shift;
+                  const int local = piece - (owner << rx_share_shift);
+                  const uint32_t at = smem_a + (uint32_t)((((seg.part << rx_share_shift) + local) * Cfg::kBlockM + my_row) * 16);
+                  st_cluster_v4(map_to_cta(at, (uint32_t)owner * G + cta_rank), v[0], v[1], v[2], v[3]);
+                }
+              }
+              return;
+            }
             if (writes_partial) {
               if (row_live) {
                 float4* dst = reinterpret_cast<float4*>(p.sk_partials + my_partial * partial_floats) +
@@ -968,14 +1023,59 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
         }
       }
       if constexpr (kSplitK) {
-        if (ok && writes_partial) {
+        if (ok && cluster_split) {
+          if constexpr (Cfg::kHalves == 1) {
+            static_assert(!kSplitK || Cfg::kHalves != 1 || kStages * Cfg::kStageBytes >= Cfg::kBlockM * Cfg::kBlockN * 4,
+                          "the operand ring must hold one CTA's fp32 partial tile");
+            // All of this warp's pieces are on their way: tell every contributor, wait for all of
+            // theirs, then sum this CTA's share in contributor order and store it.
+            __syncwarp();
+            if ((int)lane < sk_factor)
+              mbar_arrive_cluster_release(map_to_cta(bar_base + kRxDoneOff, lane * G + cta_rank));
+            ok = wait_bounded(bar_base + kRxDoneOff, 0u, ctx, kStatusTimeoutPartial + 2);
+            if (!ok) break;
+            fence_acq_rel_cluster();
+            const int share = 1 << rx_share_shift;                // pieces (of 4 columns) in this CTA's share
+            const int row = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + my_row;
+            const int col_first = n_tile * Cfg::kBlockN + seg.part * share * 4;
+            if (row < p.M && !(kDebug && (dbg & kDebugSkipStores))) {
+              uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)row * p.ldc + col_first;
+              const float4* rx = reinterpret_cast<const float4*>(smem) + my_row;
+#pragma unroll 1
+              for (int l = 0; l < share; l += 2) {                 // two pieces = 8 columns = 16 bytes of C
+                const int col = col_first + l * 4;
+                if (col >= p.N) break;
+                float4 s0 = rx[(size_t)l * Cfg::kBlockM], s1 = rx[(size_t)(l + 1) * Cfg::kBlockM];
+#pragma unroll 1
+                for (int i = 1; i < sk_factor; ++i) {
+                  const float4 t0 = rx[(size_t)(i * share + l) * Cfg::kBlockM];
+                  const float4 t1 = rx[(size_t)(i * share + l + 1) * Cfg::kBlockM];
+                  s0.x += t0.x, s0.y += t0.y, s0.z += t0.z, s0.w += t0.w;
+                  s1.x += t1.x, s1.y += t1.y, s1.z += t1.z, s1.w += t1.w;
+                }
+                const uint32_t w0 = pack2<Cfg::kIsBf16>(__float_as_uint(s0.x), __float_as_uint(s0.y));
+                const uint32_t w1 = pack2<Cfg::kIsBf16>(__float_as_uint(s0.z), __float_as_uint(s0.w));
+                const uint32_t w2 = pack2<Cfg::kIsBf16>(__float_as_uint(s1.x), __float_as_uint(s1.y));
+                const uint32_t w3 = pack2<Cfg::kIsBf16>(__float_as_uint(s1.z), __float_as_uint(s1.w));
+                if (col + 8 <= p.N) {
+                  *reinterpret_cast<uint4*>(crow + l * 4) = make_uint4(w0, w1, w2, w3);
+                } else {
+                  const uint32_t w[4] = {w0, w1, w2, w3};
+#pragma unroll
+                  for (int t2 = 0; t2 < 8; ++t2)
+                    if (col + t2 < p.N) crow[l * 4 + t2] = (uint16_t)(w[t2 >> 1] >> (16 * (t2 & 1)));
+                }
+              }
+            }
+          }
+        } else if (ok && writes_partial) {
           // Publish this warp's share of the partial tile: writes, fence, then one arrival.
           __threadfence();
           __syncwarp();
           if (lane == 0) atomicAdd(p.sk_flags + (even ? (size_t)seg.tile * G + cta_rank : (size_t)blockIdx.x), 1u);
         }
         if constexpr (Cfg::kHalves == 1) {
-          if (ok && even) {
+          if (ok && even && !cluster_split) {
             // Every contributor of the tile has arrived once all their epilogue warps have: then this
             // one reduces and stores its share, the 32-row x 64-column blocks b with b % factor == part,
             // adding the partial tiles in range order.  Plain 16-byte stores from registers.
@@ -1078,8 +1178,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   }
   tc_fence_before_sync();
   __syncthreads();
-  if constexpr (G == 2) {
-    // The peer's shared memory and barriers are MMA / commit targets until both are here.
+  if (G == 2 || cluster_split) {
+    // The peer's shared memory and barriers are MMA / commit targets until both are here; in the
+    // cluster K-split every CTA's shared memory is a store target of the whole cluster.
     cluster_arrive();
     cluster_wait();
   }
