@@ -92,12 +92,14 @@ std::atomic<long> g_opt_max_ctas{0};
 std::atomic<long> g_opt_debug_flags{0};
 std::atomic<long> g_opt_group_m{0};
 std::atomic<long> g_opt_k_rotate{-1};   // 0 never, 1 always, -1 (default) when there is a single tile row: 3 % on the few-row shapes, 2 = serpentine
-std::atomic<long> g_opt_sk_cluster{-1};  // cluster K-split (partial sums through distributed shared memory): -1 planner, 0 never, 1 always where an even split of 2, 4 or 8 is made
+std::atomic<long> g_opt_sk_cluster{-1};  // cluster K-split (partial sums through distributed shared memory): -1 planner, 0 never, 1 always where an even split of 2 or 4 is made
 std::atomic<long> g_opt_pdl{1};        // 1: launch with programmatic stream serialization (overlap with the previous kernel's tail)
 std::atomic<long> g_opt_early_prefetch{1};   // with pdl: L2 prefetch of the first stages before waiting for the previous kernel
 std::atomic<long> g_opt_tiles_n{0};    // > 0: force this many tiles per tile row (tests), when the configuration allows the widths
 std::atomic<long> g_opt_balance{1};    // 1: the planner may choose a balanced column tiling; 0: uniform tiles only
 std::atomic<long> g_opt_split_k{-1};   // -1 automatic, 0 never, 1 whenever the configuration allows it
+// Clusters of 2, 4 and 8 CTAs (one CTA per SM) the device holds at once, from the occupancy query.
+std::atomic<int> g_held_clusters[3] = {};
 // Bumped by every gemm_sm100_set_option: cached plans of an older generation are stale.
 std::atomic<unsigned> g_opt_generation{1};
 
@@ -271,6 +273,32 @@ int device_state(DeviceState** out, int* cuda_error_out) {
     if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
     st.status_ptr = static_cast<unsigned int*>(p);
     st.device = dev;
+    // How many clusters of 2, 4 and 8 one-CTA-per-SM blocks the device holds at once (host-side
+    // occupancy queries): the planner's wave count for the cluster K-split.
+    {
+      using Cfg = ConfigOf<2, true>;
+      auto kernel = gemm_tn_kernel<Cfg, false, true>;
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) == cudaSuccess) {
+        for (int i = 0; i < 3; ++i) {
+          const unsigned size = 2u << i;
+          cudaLaunchConfig_t qc = {};
+          qc.gridDim = dim3(static_cast<unsigned>(st.sm_count) / size * size);
+          qc.blockDim = dim3(Cfg::kThreads);
+          qc.dynamicSmemBytes = Cfg::kSmemBytes;
+          cudaLaunchAttribute qa[1];
+          qa[0].id = cudaLaunchAttributeClusterDimension;
+          qa[0].val.clusterDim.x = size;
+          qa[0].val.clusterDim.y = 1;
+          qa[0].val.clusterDim.z = 1;
+          qc.attrs = qa;
+          qc.numAttrs = 1;
+          int clusters = 0;
+          if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &qc) == cudaSuccess && clusters > 0)
+            g_held_clusters[i] = clusters;
+        }
+      }
+      (void)cudaGetLastError();
+    }
     // No memset: a __device__ variable without an initialiser starts at zero when its module is
     // loaded, so the first call on a device issues no synchronous work (it may come while another
     // stream is being captured).
@@ -356,7 +384,7 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // tiles written, the wait for the other contributors, one tile's worth of partial data read back
 // and stored; little of it overlaps the next unit's main loop).
 constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
-// The same for the cluster K-split (2, 4 or 8 ranges per tile, the contributors of a tile in one
+// The same for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile in one
 // cluster, partial sums exchanged through distributed shared memory: no workspace, no counters, no
 // trip through L2).
 constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {20.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
@@ -364,6 +392,9 @@ constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {20.0, 0.0, 16.0, 0.0,
 // Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
 // one GPC, and a GPC of this generation has about 18 SMs.
 inline long resident_clusters(int sm_count, int cluster_ctas) {
+  // what the occupancy query said for this process's device (filled with the device state)
+  const int index = cluster_ctas == 2 ? 0 : (cluster_ctas == 4 ? 1 : (cluster_ctas == 8 ? 2 : -1));
+  if (index >= 0 && g_held_clusters[index].load() > 0) return g_held_clusters[index].load();
   const int gpcs = sm_count >= 36 ? sm_count / 18 : 1;
   const int per_gpc = sm_count / gpcs;
   const long n = static_cast<long>(gpcs) * (per_gpc / cluster_ctas);
@@ -566,7 +597,7 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
       for (int f = 2; f <= kMaxEvenSplit; ++f) {
         if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
         if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
-        if (sk_cluster != 1 || (f != 2 && f != 4 && f != 8) || f * c.cta_group > 8) {
+        if (sk_cluster != 1 || (f != 2 && f != 4)) {
           const double c_f = static_cast<double>(ceil_div(tiles * f, slots)) *
                              (static_cast<double>(k_blocks) / f + boundary + kEvenSplitFixupKBlocks[i]) * block_n / rate;
           if (c_f < even_cost) {
@@ -575,8 +606,9 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
             even_cluster = false;
           }
         }
-        if (sk_cluster != 0 && (f == 2 || f == 4 || f == 8) && f * c.cta_group <= 8 &&   // portable cluster sizes
-            tiles * f * c.cta_group <= 65535) {
+        // 2 or 4 contributors per tile: clusters of up to 8 CTAs, and every chunk that leaves a CTA has
+        // a staging slot of its own in shared memory
+        if (sk_cluster != 0 && (f == 2 || f == 4) && tiles * f * c.cta_group <= 65535) {
           // one unit per CTA (pair), as many waves of clusters as that takes
           const long held = resident_clusters(sm_count, f * c.cta_group);
           const double c_f = static_cast<double>(ceil_div(tiles, held)) *
@@ -745,6 +777,9 @@ int ensure_config(DeviceState& st, int* cuda_error_out) {
     e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmemBytes);
     if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
+    e = cudaFuncSetAttribute(gemm_tn_kernel<Cfg, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes);
+    if (e != cudaSuccess) return set_cuda_error(cuda_error_out, e);
   }
   if constexpr (has_fanout(kCfgIndex)) {
     e = cudaFuncSetAttribute(gemm_tn_fanout_kernel<Cfg, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -811,7 +846,7 @@ int launch_config(const Problem& p, const Plan& plan, void* workspace, DeviceSta
   const bool debug = trace.ptr != nullptr || g_opt_debug_flags.load() != 0;
   auto kernel = debug ? gemm_tn_kernel<Cfg, true> : gemm_tn_kernel<Cfg, false>;
   if constexpr (has_split_k(kCfgIndex)) {
-    if (plan.split_k) kernel = gemm_tn_kernel<Cfg, false, true>;
+    if (plan.split_k) kernel = (trace.ptr && plan.cluster) ? gemm_tn_kernel<Cfg, true, true> : gemm_tn_kernel<Cfg, false, true>;
   }
   cudaError_t e;
 
@@ -1234,6 +1269,16 @@ int gemm_sm100_workspace_unregister(void* workspace) {
       return GEMM_SM100_OK;
     }
   return GEMM_SM100_ERR_WORKSPACE;
+}
+
+int gemm_sm100_resident_clusters(int cluster_ctas) {
+  DeviceState* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (device_state(&st, nullptr) != GEMM_SM100_OK) return -1;
+  }
+  if (cluster_ctas != 2 && cluster_ctas != 4 && cluster_ctas != 8) return -1;
+  return static_cast<int>(resident_clusters(st->sm_count, cluster_ctas));
 }
 
 int gemm_sm100_set_option(const char* name, long value) {

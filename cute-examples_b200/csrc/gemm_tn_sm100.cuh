@@ -91,7 +91,7 @@ struct TileParams {
   int sk_rows;                     // rows kept per partial tile: 128, or M rounded up to 32 when M < 128
   int sk_factor;                   // <= 1: contiguous ranges; > 1: every tile cut into this many equal K ranges
                                    // (then one partial tile per unit and CTA of the pair, one counter per tile and CTA)
-  // > 0 (even split with sk_factor 2, 4 or 8, launched in clusters of sk_factor CTA (pair)s, one unit
+  // > 0 (even split with sk_factor 2 or 4, launched in clusters of sk_factor CTA (pair)s, one unit
   // per CTA (pair)): the contributors of a tile sit in one cluster and exchange their partial sums
   // through distributed shared memory instead of the workspace, which is then not used at all.
   int sk_cluster;
@@ -131,6 +131,8 @@ enum : int {
   kTraceTiles = 11,       // tiles this CTA processed
   kTraceTimeEntryNs = 12, // %globaltimer at entry
   kTraceTimeExitNs = 13,  // %globaltimer at exit
+  kTraceRxReady = 14,     // cluster K-split: every contributor's ring is idle (epilogue warp 2)
+  kTraceRxDone = 15,      // cluster K-split: every contributor's partial sums have arrived (epilogue warp 2)
   kTraceWords = 16,
 };
 
@@ -461,9 +463,15 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       // every epilogue warp of every contributor to this CTA's rows arrives once on each
       const uint32_t arrivals = (uint32_t)(Cfg::kEpiWarps * (p.sk_cluster > 0 ? p.sk_factor : 1));
       mbar_init(bar_base + kRxReadyOff, arrivals);
-      mbar_init(bar_base + kRxDoneOff, arrivals);
+      // the other contributors' copies into this CTA's receive area are counted in bytes
+      mbar_init(bar_base + kRxDoneOff, 1);
     }
     fence_mbar_init();
+    if constexpr (kSplitK) {
+      if (p.sk_cluster > 0)
+        mbar_arrive_expect_tx(bar_base + kRxDoneOff,
+                              (uint32_t)(Cfg::kBlockM * Cfg::kBlockN * 4 / p.sk_factor * (p.sk_factor - 1)));
+    }
   }
   // Barriers are initialised: let the producer go.  The TMEM allocation (slow for a CTA pair)
   // happens after this point, off the path of the first operand loads.
@@ -775,7 +783,11 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     // cluster K-split: a contributor's share of the tile's 16-byte pieces (kBlockN / 4 of them) is
     // 2^rx_share_shift pieces wide
     int rx_share_shift = 0;
-    if constexpr (kSplitK) {
+    int remote_chunks = 0;                                   // chunks this warp has sent to other CTAs so far
+    constexpr uint32_t kRxBytes = Cfg::kBlockM * Cfg::kBlockN * 4;   // receive area: one fp32 partial tile, at the start of the ring
+    if constexpr (kSplitK && Cfg::kHalves == 1) {
+      static_assert(Cfg::kEpiWarps != 4 || kStages * Cfg::kStageBytes + Cfg::kEpiBytes >= (int)kRxBytes + 4 * 3 * 8192,
+                    "ring + epilogue staging must hold the receive area and three staging slots per warp");
       if (cluster_split)
         while (((Cfg::kBlockN / 4) >> rx_share_shift) > sk_factor) ++rx_share_shift;
     }
@@ -836,6 +848,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               break;
             }
             fence_acq_rel_cluster();
+            if constexpr (kDebug)
+              if (trace && warp == 2 && lane == 0) trace[kTraceRxReady] = clock64();
           }
         }
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + slot * Cfg::kSlotCols;
@@ -844,18 +858,31 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           if constexpr (kSplitK) {
             const int piece0 = (h * kChunks + c) * 16;       // first 16-byte piece of this chunk
             if (cluster_split) {
-              // 16-byte piece P of the tile's columns belongs to contributor P / share; it goes into
-              // that CTA's ring, laid out [sender][piece of the share][row], 16 bytes each.
-              if (row_live) {
+              // The chunk belongs to the share of contributor `owner`.  Its receive area is laid out
+              // [sender][row quarter][piece of the share][row][16 bytes], so what one warp sends
+              // for one chunk is 8 KB in one piece: written to a staging slot of its own (every
+              // chunk that leaves the CTA has one, nothing is reused) and moved by one asynchronous
+              // copy that is counted on the owner's barrier.  The own share goes straight into place.
+              const int owner = piece0 >> rx_share_shift;
+              const int local0 = piece0 - (owner << rx_share_shift);
+              const uint32_t rx_off = (uint32_t)((((seg.part * 4 + q) << rx_share_shift) + local0) * 512);
+              uint32_t dst = smem_a + rx_off;
+              if (owner != seg.part) dst = smem_a + kRxBytes + (uint32_t)(q * 3 + remote_chunks) * 8192u;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const uint32_t* v = (j < 8) ? &v0[4 * j] : &v1[4 * (j - 8)];
-                  const int piece = piece0 + j;
-                  const int owner = piece >> rx_share_shift;
-                  const int local = piece - (owner << rx_share_shift);
-                  const uint32_t at = smem_a + (uint32_t)((((seg.part << rx_share_shift) + local) * Cfg::kBlockM + my_row) * 16);
-                  st_cluster_v4(map_to_cta(at, (uint32_t)owner * G + cta_rank), v[0], v[1], v[2], v[3]);
-                }
+              for (int j = 0; j < 16; ++j) {
+                const uint32_t* v = (j < 8) ? &v0[4 * j] : &v1[4 * (j - 8)];
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + j * 512u + lane * 16u), "r"(v[0]),
+                             "r"(v[1]), "r"(v[2]), "r"(v[3])
+                             : "memory");
+              }
+              if (owner != seg.part) {
+                ++remote_chunks;
+                fence_proxy_async_smem();
+                __syncwarp();
+                const uint32_t to = (uint32_t)owner * G + cta_rank;
+                if (lane == 0)
+                  bulk_copy_smem_to_cluster(map_to_cta(smem_a + rx_off, to), dst, 8192u,
+                                            map_to_cta(bar_base + kRxDoneOff, to));
               }
               return;
             }
@@ -1025,33 +1052,39 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       if constexpr (kSplitK) {
         if (ok && cluster_split) {
           if constexpr (Cfg::kHalves == 1) {
-            static_assert(!kSplitK || Cfg::kHalves != 1 || kStages * Cfg::kStageBytes >= Cfg::kBlockM * Cfg::kBlockN * 4,
-                          "the operand ring must hold one CTA's fp32 partial tile");
-            // All of this warp's pieces are on their way: tell every contributor, wait for all of
-            // theirs, then sum this CTA's share in contributor order and store it.
-            __syncwarp();
-            if ((int)lane < sk_factor)
-              mbar_arrive_cluster_release(map_to_cta(bar_base + kRxDoneOff, lane * G + cta_rank));
+            // Wait for the other contributors' copies (counted in bytes), then sum this CTA's share
+            // in contributor order and store it.
             ok = wait_bounded(bar_base + kRxDoneOff, 0u, ctx, kStatusTimeoutPartial + 2);
             if (!ok) break;
-            fence_acq_rel_cluster();
+            if constexpr (kDebug)
+              if (trace && warp == 2 && lane == 0) trace[kTraceRxDone] = clock64();
             const int share = 1 << rx_share_shift;                // pieces (of 4 columns) in this CTA's share
             const int row = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + my_row;
             const int col_first = n_tile * Cfg::kBlockN + seg.part * share * 4;
             if (row < p.M && !(kDebug && (dbg & kDebugSkipStores))) {
               uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)row * p.ldc + col_first;
-              const float4* rx = reinterpret_cast<const float4*>(smem) + my_row;
+              // [sender][row quarter][piece][row]: this thread's row of piece l from sender i
+              const float4* rx = reinterpret_cast<const float4*>(smem) + ((size_t)(q * share) * 32 + lane);
+              const size_t sender_stride = (size_t)4 * share * 32;
 #pragma unroll 1
               for (int l = 0; l < share; l += 2) {                 // two pieces = 8 columns = 16 bytes of C
                 const int col = col_first + l * 4;
                 if (col >= p.N) break;
-                float4 s0 = rx[(size_t)l * Cfg::kBlockM], s1 = rx[(size_t)(l + 1) * Cfg::kBlockM];
-#pragma unroll 1
-                for (int i = 1; i < sk_factor; ++i) {
-                  const float4 t0 = rx[(size_t)(i * share + l) * Cfg::kBlockM];
-                  const float4 t1 = rx[(size_t)(i * share + l + 1) * Cfg::kBlockM];
-                  s0.x += t0.x, s0.y += t0.y, s0.z += t0.z, s0.w += t0.w;
-                  s1.x += t1.x, s1.y += t1.y, s1.z += t1.z, s1.w += t1.w;
+                const float4* r0 = rx + (size_t)l * 32;
+                const float4* r1 = r0 + 32;
+                float4 s0 = r0[0], s1 = r1[0];
+                {
+                  const float4 a0 = r0[sender_stride], a1 = r1[sender_stride];
+                  s0.x += a0.x, s0.y += a0.y, s0.z += a0.z, s0.w += a0.w;
+                  s1.x += a1.x, s1.y += a1.y, s1.z += a1.z, s1.w += a1.w;
+                }
+                if (sk_factor == 4) {
+                  const float4 b0 = r0[2 * sender_stride], b1 = r1[2 * sender_stride];
+                  const float4 c0 = r0[3 * sender_stride], c1 = r1[3 * sender_stride];
+                  s0.x += b0.x, s0.y += b0.y, s0.z += b0.z, s0.w += b0.w;
+                  s1.x += b1.x, s1.y += b1.y, s1.z += b1.z, s1.w += b1.w;
+                  s0.x += c0.x, s0.y += c0.y, s0.z += c0.z, s0.w += c0.w;
+                  s1.x += c1.x, s1.y += c1.y, s1.z += c1.z, s1.w += c1.w;
                 }
                 const uint32_t w0 = pack2<Cfg::kIsBf16>(__float_as_uint(s0.x), __float_as_uint(s0.y));
                 const uint32_t w1 = pack2<Cfg::kIsBf16>(__float_as_uint(s0.z), __float_as_uint(s0.w));

@@ -114,6 +114,16 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
                : "memory");
 }
 
+// Asynchronous copy of `bytes` (a multiple of 16) from this CTA's shared memory into the shared
+// memory of a CTA of the cluster; the bytes are counted on an mbarrier of the destination CTA.
+__device__ __forceinline__ void bulk_copy_smem_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                          uint32_t mbar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster),
+               "r"(src_cta), "r"(bytes), "r"(mbar_cluster)
+               : "memory");
+}
+
 // Arrive without release ordering (experiments that only count arrivals).
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)

@@ -104,16 +104,18 @@ def bench_shape(M, N, K, dtype, scratch, peak, layout="tn"):
     return rec
 
 
-OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0, "pdl": 1, "early_prefetch": 1}
+OPTION_DEFAULTS = {"tile_config": -1, "split_k": -1, "group_m": 0, "k_rotate": -1, "max_ctas": 0, "balance": 1, "tiles_n": 0, "pdl": 1, "early_prefetch": 1, "sk_cluster": -1}
 
 KSPLIT_SHAPES = ("512x4096x4096,1024x4096x4096,256x8192x8192,256x512x65536,512x512x32768,1024x1024x16384,"
                  "2048x2048x8192,1024x2048x8192,512x4096x8192,128x2048x16384,256x256x32768,1024x1024x4096,"
                  "2048x1024x4096,512x1024x65536")
 KSPLIT_VARIANTS = ("c0:tile_config=0,split_k=0;c3:tile_config=3,split_k=0;c2s:tile_config=2,split_k=1;"
-                   "c0e2:tile_config=0,split_k=2;c0e4:tile_config=0,split_k=4;c0e8:tile_config=0,split_k=8;"
-                   "c0e16:tile_config=0,split_k=16;"
-                   "c2e2:tile_config=2,split_k=2;c2e4:tile_config=2,split_k=4;c2e8:tile_config=2,split_k=8;"
-                   "c2e16:tile_config=2,split_k=16;auto;mm")
+                   "c0e2:tile_config=0,split_k=2,sk_cluster=0;c0e4:tile_config=0,split_k=4,sk_cluster=0;"
+                   "c0e8:tile_config=0,split_k=8;c0e16:tile_config=0,split_k=16;"
+                   "c2e2:tile_config=2,split_k=2,sk_cluster=0;c2e4:tile_config=2,split_k=4,sk_cluster=0;"
+                   "c2e8:tile_config=2,split_k=8;c2e16:tile_config=2,split_k=16;"
+                   "c0k2:tile_config=0,split_k=2,sk_cluster=1;c0k4:tile_config=0,split_k=4,sk_cluster=1;"
+                   "c2k2:tile_config=2,split_k=2,sk_cluster=1;c2k4:tile_config=2,split_k=4,sk_cluster=1;auto;mm")
 
 
 def parse_variants(text):

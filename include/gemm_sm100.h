@@ -17,7 +17,7 @@
  * synchronisation).  A host that captures CUDA graphs should call gemm_sm100_init() once per
  * device before its first capture, which does all of that up front.
  *
- * Co-residency.  The K-split schedules (gemm_sm100_workspace_bytes() > 0, or the "split_k"
+ * Co-residency.  The K-split schedules that use a workspace (gemm_sm100_workspace_bytes() > 0, or the "split_k"
  * option, or gemm_sm100_tn_static_scratch) let CTAs wait for partial sums of other CTAs of the
  * same grid, so the whole grid must be resident at once.  The grid is sized from the device's SM
  * count; a host that gives this library only part of the SMs (an SM-limited or "green" context,
@@ -163,6 +163,12 @@ int gemm_sm100_workspace_register(void* workspace, size_t workspace_bytes, void*
 /* Forgets a registered workspace (GEMM_SM100_ERR_WORKSPACE if it was not registered). */
 int gemm_sm100_workspace_unregister(void* workspace);
 
+/* How many thread-block clusters of `cluster_ctas` (2, 4 or 8) CTAs of this library's kernels
+ * (one CTA per SM) the current device holds at once, from the CUDA occupancy query; what the
+ * planner divides by when it counts the waves of a cluster K-split.  Negative on error.  No
+ * reference counterpart. */
+int gemm_sm100_resident_clusters(int cluster_ctas);
+
 /* Number of SMs of the current device (the persistent grid is sized from it; the
  * reference hard-codes 132, gemm_test.cu:72).  Returns a negative value on error. */
 int gemm_sm100_num_sms(void);
@@ -184,6 +190,11 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  *                  pair, whenever the chosen configuration has a K-split variant; 2..16 = every
  *                  tile cut into that many equal K ranges with the reduction spread over the
  *                  contributors (256 x 256 and 128 x 256 tiles).
+ *   "sk_cluster"   how the contributors of a tile cut into 2 or 4 K ranges exchange their partial
+ *                  sums: 1 = always inside a thread-block cluster (one cluster per tile, one range
+ *                  per CTA or pair, partial tiles moved between the CTAs' shared memories by
+ *                  asynchronous bulk copies; needs no workspace and no co-residency of the grid);
+ *                  0 = always through the workspace; -1 = the planner decides (default).
  *   "balance"      1 = the planner may give a tile row a number of tiles that fills the SMs evenly,
  *                  with tile widths in steps of 64 columns (default); 0 = uniform tiles only.
  *   "pdl"          1 = launch with the programmatic-stream-serialization attribute (default): when

@@ -65,6 +65,8 @@ def load_capi() -> ctypes.CDLL:
     lib.gemm_sm100_workspace_register.restype = I
     lib.gemm_sm100_workspace_unregister.argtypes = [P]
     lib.gemm_sm100_workspace_unregister.restype = I
+    lib.gemm_sm100_resident_clusters.argtypes = [I]
+    lib.gemm_sm100_resident_clusters.restype = I
     lib.gemm_sm100_num_sms.argtypes = []
     lib.gemm_sm100_num_sms.restype = I
     lib.gemm_sm100_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(I)]

@@ -38,6 +38,7 @@ def _reset_options(capi):
     capi.gemm_sm100_set_option(b"tile_config", -1)
     capi.gemm_sm100_set_option(b"max_ctas", 0)
     capi.gemm_sm100_set_option(b"split_k", -1)
+    capi.gemm_sm100_set_option(b"sk_cluster", -1)
     capi.gemm_sm100_set_option(b"k_rotate", -1)
     capi.gemm_sm100_set_option(b"group_m", 0)
     capi.gemm_sm100_set_option(b"tiles_n", 0)
@@ -358,6 +359,7 @@ def test_even_split_matches_oracle(capi, shape, factor, config):
     A, B = oracle.make_inputs(M, N, K, 160 + M % 7)
     capi.gemm_sm100_set_option(b"tile_config", config)
     capi.gemm_sm100_set_option(b"split_k", factor)
+    capi.gemm_sm100_set_option(b"sk_cluster", 0)          # partial sums through the workspace
     capi.gemm_sm100_set_option(b"max_ctas", max_ctas)
     assert capi.gemm_sm100_workspace_bytes(M, N, K, 0) > 0
     C = run_capi(capi, A, B)
@@ -375,6 +377,7 @@ def test_even_split_many_ranges(capi, config, factor):
     M, N, K = 300, 520, 64 * 8 * factor + 64
     capi.gemm_sm100_set_option(b"tile_config", config)
     capi.gemm_sm100_set_option(b"split_k", factor)
+    capi.gemm_sm100_set_option(b"sk_cluster", 0)          # partial sums through the workspace
     assert "K ranges" in plan_text(capi, M, N, K)
     A, B = oracle.make_inputs(M, N, K, 240 + factor)
     C = run_capi(capi, A, B)
@@ -396,6 +399,7 @@ def test_even_split_exact_on_integers(capi, dtype, config):
     B = torch.cat([B, torch.zeros(N, K - 256, dtype=dtype)], dim=1)
     capi.gemm_sm100_set_option(b"tile_config", config)
     capi.gemm_sm100_set_option(b"split_k", 4)
+    capi.gemm_sm100_set_option(b"sk_cluster", 0)          # partial sums through the workspace
     C = run_capi(capi, A, B)
     assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
 
@@ -410,12 +414,81 @@ def test_even_split_ragged_n_inside_wider_buffer(capi):
     wide = wide0.cuda()
     capi.gemm_sm100_set_option(b"tile_config", 2)
     capi.gemm_sm100_set_option(b"split_k", 2)
+    capi.gemm_sm100_set_option(b"sk_cluster", 0)          # partial sums through the workspace
     assert capi_gemm(capi, A.cuda(), B.cuda(), wide[:, 8:8 + N], ldc=width) == 0
     assert capi_status(capi) == (0, 0)
     got = wide.cpu()
     assert torch.equal(got[:, 8:8 + N].float(), A.float() @ B.float().T)
     assert torch.equal(got[:, :8].view(torch.int16), wide0[:, :8].view(torch.int16))
     assert torch.equal(got[:, 8 + N:].view(torch.int16), wide0[:, 8 + N:].view(torch.int16))
+
+
+# configuration, ranges per tile: the contributors of a tile form one cluster (pair tile: two CTAs per contributor)
+CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4)]
+
+
+@pytest.mark.parametrize("config,factor", CLUSTER_SPLITS)
+@pytest.mark.parametrize("shape", [(256, 512, 4096), (300, 520, 2048 + 64), (100, 264, 1024), (1024, 2048, 1024)])
+def test_cluster_split_matches_oracle_and_global_split(capi, config, factor, shape):
+    """Even K-split whose partial sums travel through distributed shared memory: no workspace, one
+    unit per CTA (pair), as many waves of clusters as the tiles need (the last shape: 256 to 512
+    CTAs).  Same sums in the same order as the even split through global memory, hence the same bits."""
+    M, N, K = shape
+    if K // 64 < 8 * factor:
+        pytest.skip("fewer than 8 K blocks per range: no split is made")
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"split_k", factor)
+    capi.gemm_sm100_set_option(b"sk_cluster", 1)
+    text = plan_text(capi, M, N, K)
+    assert "one cluster per tile" in text and text.endswith("workspace=0"), text
+    assert capi.gemm_sm100_workspace_bytes(M, N, K, 0) == 0
+    A, B = oracle.make_inputs(M, N, K, 260 + factor)
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
+    assert torch.equal(C.view(torch.int16), run_capi(capi, A, B).view(torch.int16))
+    capi.gemm_sm100_set_option(b"sk_cluster", 0)
+    assert "one cluster per tile" not in plan_text(capi, M, N, K)
+    assert torch.equal(C.view(torch.int16), run_capi(capi, A, B).view(torch.int16))
+
+
+@pytest.mark.parametrize("config,factor", CLUSTER_SPLITS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_cluster_split_exact_on_integers(capi, dtype, config, factor):
+    M, N, K = 384, 1288, 64 * 8 * factor       # N % 8 == 0 but not a multiple of 64: ragged last chunk
+    A, B = oracle.make_ternary_inputs(M, N, 256, 261, dtype)
+    A = torch.cat([A, torch.zeros(M, K - 256, dtype=dtype)], dim=1)
+    B = torch.cat([B, torch.zeros(N, K - 256, dtype=dtype)], dim=1)
+    # spread the non-zero part over all ranges: permute the K axis of both operands alike
+    perm = torch.randperm(K, generator=torch.Generator().manual_seed(262))
+    A, B = A[:, perm].contiguous(), B[:, perm].contiguous()
+    capi.gemm_sm100_set_option(b"tile_config", config)
+    capi.gemm_sm100_set_option(b"split_k", factor)
+    capi.gemm_sm100_set_option(b"sk_cluster", 1)
+    assert "one cluster per tile" in plan_text(capi, M, N, K)
+    C = run_capi(capi, A, B)
+    assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
+
+
+def test_cluster_split_ragged_n_inside_wider_buffer(capi):
+    """N not a multiple of 8 inside a wider C: the columns past N keep their contents."""
+    M, N, K = 200, 259, 2048
+    A, B = oracle.make_ternary_inputs(M, N, 128, 263)
+    A = torch.cat([A, torch.zeros(M, K - 128, dtype=A.dtype)], dim=1)
+    B = torch.cat([B, torch.zeros(N, K - 128, dtype=B.dtype)], dim=1)
+    width = 264 + 16
+    wide0 = torch.randn(M, width, generator=torch.Generator().manual_seed(264)).to(torch.bfloat16)
+    for config, factor in ((2, 4), (0, 2)):
+        wide = wide0.cuda()
+        capi.gemm_sm100_set_option(b"tile_config", config)
+        capi.gemm_sm100_set_option(b"split_k", factor)
+        capi.gemm_sm100_set_option(b"sk_cluster", 1)
+        assert "one cluster per tile" in plan_text(capi, M, N, K)
+        assert capi_gemm(capi, A.cuda(), B.cuda(), wide[:, 8:8 + N], ldc=width) == 0
+        assert capi_status(capi) == (0, 0)
+        got = wide.cpu()
+        assert torch.equal(got[:, 8:8 + N].float(), A.float() @ B.float().T)
+        assert torch.equal(got[:, :8].view(torch.int16), wide0[:, :8].view(torch.int16))
+        assert torch.equal(got[:, 8 + N:].view(torch.int16), wide0[:, 8 + N:].view(torch.int16))
 
 
 def test_registered_workspace_needs_no_memset(capi):
@@ -438,6 +511,7 @@ def test_registered_workspace_needs_no_memset(capi):
         for (M, N, K), config, split in cases + cases:
             capi.gemm_sm100_set_option(b"tile_config", config)
             capi.gemm_sm100_set_option(b"split_k", split)
+            capi.gemm_sm100_set_option(b"sk_cluster", 0)          # partial sums through the workspace
             assert "K ranges" in plan_text(capi, M, N, K) or split == 1
             A, B = oracle.make_inputs(M, N, K, 250 + split)
             want = run_capi(capi, A, B)                                       # its own workspace, memset
@@ -502,6 +576,7 @@ def test_nn_layout_matches_oracle(gk, capi, config, shape):
     # K ascending in every tile: the automatic rotation of the few-row shapes starts each tile at a
     # K block that depends on the tiling, and the two entry points may tile differently
     capi.gemm_sm100_set_option(b"k_rotate", 0)
+    capi.gemm_sm100_set_option(b"split_k", 0)           # and whole tiles: the layout kernels have no K-split
     C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
     out = gk.gemm_nn(A.cuda(), B.cuda(), C)
     gk.device_status()
