@@ -146,6 +146,8 @@ def main():
     ap.add_argument("--metrics", default="full", choices=["full", "short"],
                     help="full = --set full (about 40 passes per launch); short = a dozen metrics (a few passes)")
     ap.add_argument("--kernel", default="gemm_tn", help="regex of the kernel name to capture")
+    ap.add_argument("--cublas", action="store_true",
+                    help="capture cuBLAS (torch.mm) on the same operands instead; --kernel then defaults to its GEMM kernels")
     ap.add_argument("--out", default="profile_out")
     ap.add_argument("--summarize", default=None, help="only print the table of an existing raw CSV")
     args = ap.parse_args()
@@ -172,6 +174,11 @@ def main():
               "--launches", "3", "--tile-config", str(args.tile_config)]
     for o in args.option:
         target += ["--option", o]
+    if args.cublas:
+        target.append("--cublas")
+        tag += "_cublas"
+        if args.kernel == "gemm_tn":
+            args.kernel = "nvjet|gemm|cutlass"
 
     # 1. the plain run must succeed before anything is profiled
     if run(target, os.path.join(args.out, f"plain_{tag}.log")) != 0:

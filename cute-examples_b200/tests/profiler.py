@@ -1,4 +1,5 @@
-"""Profiling target: a few launches of gemm_tn_test on one shape, nothing else.
+"""Profiling target: a few launches of gemm_tn_test (or, with --cublas, of torch.mm on the same
+operands, for a like-for-like counter comparison) on one shape, nothing else.
 
 Successor of the reference's kernels/tests/profiler.py:1-12 (one 4096 x 4096 launch meant to be
 run under Nsight).  tests/ncu_capture.py runs it under `ncu --clock-control none -k regex:gemm_tn ...`
@@ -22,6 +23,7 @@ ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
 ap.add_argument("--launches", type=int, default=3)
 ap.add_argument("--tile-config", type=int, default=-1)
 ap.add_argument("--option", action="append", default=[], help="name=value for gemm_kernels.set_option")
+ap.add_argument("--cublas", action="store_true", help="launch torch.mm(A, B.T) instead of this library's kernel")
 args = ap.parse_args()
 
 dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
@@ -34,6 +36,9 @@ A = (torch.randn((args.m, args.k), device=device) / args.k ** 0.5).to(dtype)
 B = (torch.randn((args.n, args.k), device=device) / args.k ** 0.5).to(dtype)
 C_custom = torch.empty((args.m, args.n), device=device, dtype=dtype)
 for _ in range(args.launches):
-    gemm_tn_test(A, B, C_custom)
+    if args.cublas:
+        torch.mm(A, B.T, out=C_custom)
+    else:
+        gemm_tn_test(A, B, C_custom)
 device_status()
 print("done", args.m, args.n, args.k, args.dtype)
