@@ -423,6 +423,42 @@ def test_even_split_ragged_n_inside_wider_buffer(capi):
     assert torch.equal(got[:, 8 + N:].view(torch.int16), wide0[:, 8 + N:].view(torch.int16))
 
 
+def _random_problems():
+    rng = np.random.default_rng(20240607)
+    out = []
+    for i in range(48):
+        regime = i % 3
+        if regime == 0:      # few rows, many columns
+            M, N, K = int(rng.integers(1, 129)), 8 * int(rng.integers(8, 600)), 8 * int(rng.integers(8, 1024))
+        elif regime == 1:    # few tiles, long K
+            M, N, K = int(rng.integers(100, 600)), 8 * int(rng.integers(16, 140)), 64 * int(rng.integers(32, 129))
+        else:                # several tile rows and columns, ragged everywhere
+            M, N, K = int(rng.integers(129, 2500)), 8 * int(rng.integers(16, 400)), 8 * int(rng.integers(8, 300))
+        out.append((M, N, K, i))
+    return out
+
+
+@pytest.mark.parametrize("M,N,K,index", _random_problems())
+def test_random_shapes_library_plan_exact(capi, M, N, K, index):
+    """Seeded random shapes over the three regimes the planner treats differently, every option at
+    its default (so whatever the planner picks is what runs: whole tiles, balanced widths, few-row
+    tiles, K-split through the workspace or inside clusters), operands in {-1, 0, 1} with at most
+    200 non-zero K positions: every sum is a small integer, so the result must match the fp32
+    reference product bit for bit whatever the order of summation."""
+    dtype = torch.bfloat16 if index % 2 == 0 else torch.float16
+    g = torch.Generator().manual_seed(1000 + index)
+    A = torch.randint(-1, 2, (M, K), generator=g).to(dtype)
+    B = torch.randint(-1, 2, (N, K), generator=g).to(dtype)
+    if K > 200:
+        keep = torch.zeros(K, dtype=torch.bool)
+        keep[torch.randperm(K, generator=g)[:200]] = True
+        A[:, ~keep] = 0
+        B[:, ~keep] = 0
+    C = run_capi(capi, A, B)
+    want = oracle.reference_matmul_fp32(A, B).to(dtype)
+    assert torch.equal(C.view(torch.int16), want.view(torch.int16)), plan_text(capi, M, N, K)
+
+
 # configuration, ranges per tile: the contributors of a tile form one cluster (pair tile: two CTAs per contributor)
 CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4)]
 
