@@ -384,9 +384,11 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // tiles written, the wait for the other contributors, one tile's worth of partial data read back
 // and stored; little of it overlaps the next unit's main loop).
 constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
-// The same for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile in one
-// cluster, partial sums exchanged through distributed shared memory: no workspace, no counters, no
-// trip through L2).
+// K block time of a single wave of few, independently streaming CTAs relative to the full grid's.
+constexpr double kFewTileKBlockFactor[kNumConfigs] = {1.95, 1.0, 2.15, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0};
+// The exchange's cost for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile
+// in one cluster, partial sums exchanged through distributed shared memory: no workspace, no
+// counters, no trip through L2).
 constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {20.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 
 // Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
@@ -594,31 +596,33 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     double even_cost = 1e300;
     if (allow_split && has_even_split(i) && g_opt_split_k != 0 && g_opt_split_k != 1) {
       const long sk_cluster = g_opt_sk_cluster.load();
+      // Which cut is best is decided with the K loop at the pace it has when few CTAs (pairs) each
+      // stream their own operands (measured: about twice the K block time of a full grid, while the
+      // cost of the exchange stays what it is); whether to cut at all, below, with the same units as
+      // the whole-tile cost.  With full-grid K block times four contributors in a cluster were
+      // preferred to eight through the workspace, which measured 4 us faster on
+      // 512..2048 x 128..2048 x 8192.
+      const double few = kFewTileKBlockFactor[i];
+      double best_score = 1e300;
+      auto consider = [&](int f, bool cluster, long waves_f, double fixup) {
+        const double per_wave = static_cast<double>(k_blocks) / f + boundary + fixup;
+        const double score = static_cast<double>(waves_f) * (per_wave + (few - 1.0) * k_blocks / f);
+        if (score < best_score) {
+          best_score = score;
+          even_cost = static_cast<double>(waves_f) * per_wave * block_n / rate;
+          even_s = f;
+          even_cluster = cluster;
+        }
+      };
       for (int f = 2; f <= kMaxEvenSplit; ++f) {
         if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
         if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
-        if (sk_cluster != 1 || (f != 2 && f != 4)) {
-          const double c_f = static_cast<double>(ceil_div(tiles * f, slots)) *
-                             (static_cast<double>(k_blocks) / f + boundary + kEvenSplitFixupKBlocks[i]) * block_n / rate;
-          if (c_f < even_cost) {
-            even_cost = c_f;
-            even_s = f;
-            even_cluster = false;
-          }
-        }
+        if (sk_cluster != 1 || (f != 2 && f != 4)) consider(f, false, ceil_div(tiles * f, slots), kEvenSplitFixupKBlocks[i]);
         // 2 or 4 contributors per tile: clusters of up to 8 CTAs, and every chunk that leaves a CTA has
-        // a staging slot of its own in shared memory
-        if (sk_cluster != 0 && (f == 2 || f == 4) && tiles * f * c.cta_group <= 65535) {
-          // one unit per CTA (pair), as many waves of clusters as that takes
-          const long held = resident_clusters(sm_count, f * c.cta_group);
-          const double c_f = static_cast<double>(ceil_div(tiles, held)) *
-                             (static_cast<double>(k_blocks) / f + boundary + kClusterSplitFixupKBlocks[i]) * block_n / rate;
-          if (c_f < even_cost) {
-            even_cost = c_f;
-            even_s = f;
-            even_cluster = true;
-          }
-        }
+        // a staging slot of its own in shared memory; one unit per CTA (pair), as many waves of
+        // clusters as that takes
+        if (sk_cluster != 0 && (f == 2 || f == 4) && tiles * f * c.cta_group <= 65535)
+          consider(f, true, ceil_div(tiles, resident_clusters(sm_count, f * c.cta_group)), kClusterSplitFixupKBlocks[i]);
       }
     }
     const double best_other = (can_split && auto_split) ? split_cost : cost;
