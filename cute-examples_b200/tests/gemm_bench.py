@@ -221,6 +221,62 @@ def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None, coold
         del A, B, C, outs
 
 
+def sweep(dtype):
+    """Grid of shapes (M, N in 128..8192, K in 512..32768, at most 8192^3 flops), the library's own
+    plan against cuBLAS (torch.mm) in alternation, three rounds each of back-to-back launches
+    (operands stay in L2 where they fit); prints the worst and best ratios, the geometric mean and
+    a Markdown table of all shapes by K."""
+    import math
+
+    def timed_us(fn, iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) * 1e3 / iters
+
+    dims = [128, 256, 512, 1024, 2048, 4096, 8192]
+    rows = []
+    for K in (512, 2048, 8192, 32768):
+        for M in dims:
+            for N in dims:
+                if M * N * K > 8192 ** 3 or (K == 32768 and M * N > 2048 * 2048):
+                    continue
+                A = (torch.randn(M, K, device="cuda") / K ** 0.5).to(dtype)
+                B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(dtype)
+                C, C2 = torch.empty(M, N, dtype=dtype, device="cuda"), torch.empty(M, N, dtype=dtype, device="cuda")
+                iters = max(5, min(100, int(2e4 / max(1.0, 2.0 * M * N * K / 1.2e9))))
+                ours, mm = [], []
+                for _ in range(3):
+                    ours.append(timed_us(lambda: gk.gemm_tn_test(A, B, C), iters))
+                    mm.append(timed_us(lambda: torch.mm(A, B.T, out=C2), iters))
+                o, m = statistics.median(ours), statistics.median(mm)
+                rows.append((o / m, M, N, K, o, m, gk.describe_plan(M, N, K, 0 if dtype == torch.bfloat16 else 1)))
+                del A, B, C, C2
+    gk.device_status()
+    ranked = sorted(rows, reverse=True)
+    print("ours / cuBLAS time, worst 15:")
+    for r in ranked[:15]:
+        print(f"  {r[0]:.2f}  {r[1]}x{r[2]}x{r[3]}  ours {r[4]:.1f} us  cuBLAS {r[5]:.1f} us  | {r[6].split(';')[0]};{r[6].split(';')[1]}")
+    print("best 8:")
+    for r in ranked[-8:]:
+        print(f"  {r[0]:.2f}  {r[1]}x{r[2]}x{r[3]}  ours {r[4]:.1f} us  cuBLAS {r[5]:.1f} us")
+    print(f"geometric mean of ours / cuBLAS over {len(rows)} shapes: {math.exp(sum(math.log(r[0]) for r in rows) / len(rows)):.3f}")
+    for K in (512, 2048, 8192, 32768):
+        sub = {(r[1], r[2]): r[0] for r in rows if r[3] == K}
+        if not sub:
+            continue
+        print(f"\nK = {K}: ours / cuBLAS time (rows M, columns N)\n")
+        print("| M \\ N | " + " | ".join(str(n) for n in dims) + " |")
+        print("|---|" + "---|" * len(dims))
+        for M in dims:
+            print(f"| {M} | " + " | ".join(f"{sub[(M, N)]:.2f}" if (M, N) in sub else "" for N in dims) + " |")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
@@ -235,8 +291,13 @@ def main():
                     help="A/B mode: idle seconds before every measurement (burst regime instead of the power-capped one)")
     ap.add_argument("--ksplit-table", action="store_true", help="A/B mode preset: K-split schedules on few-tile problems")
     ap.add_argument("--fanout", default=None, help="A/B mode on gemm_tn_fanout with these output counts (local buffers)")
+    ap.add_argument("--sweep", action="store_true", help="grid of shapes against cuBLAS, worst / best ratios and geometric mean")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    if args.sweep:
+        print(f"device: {torch.cuda.get_device_name()}  SMs: {gk.num_sms()}")
+        sweep(dtype)
+        return
     if args.ksplit_table:
         args.ab = args.ab or KSPLIT_VARIANTS
         args.shapes = args.shapes or KSPLIT_SHAPES
