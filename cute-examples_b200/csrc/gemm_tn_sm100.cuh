@@ -137,7 +137,7 @@ enum : int {
 };
 
 template <int kCtaGroup_, int kMmaN_, int kHalves_, int kStages_, int kEpiWarps_, bool kIsBf16_, int kARows_ = 128,
-          int kEpiBufs_ = 0>
+          int kEpiBufs_ = 0, int kKSub_ = 1>
 struct GemmConfig {
   static constexpr int kCtaGroup = kCtaGroup_;
   static constexpr int kBlockM = 128;              // rows of the accumulator (and of the MMA's A operand) per CTA
@@ -155,7 +155,13 @@ struct GemmConfig {
   //               an epilogue that is only partly hidden.
   static constexpr int kHalves = kHalves_;
   static constexpr int kBlockN = kMmaN * kHalves;  // columns of C per tile (whole pair)
-  static constexpr int kBlockK = 64;               // 64 x 16 bit = one 128-byte swizzle row
+  // K elements per stage: kKSub blocks of 64 (64 x 16 bit = one 128-byte swizzle row).  With two, a
+  // stage's operand tiles are each loaded by ONE TMA instruction (a 3-D box: 64 elements x rows x 2 K
+  // blocks, landing as two ordinary K-major tiles one after the other): an SM's TMA takes about 130
+  // cycles per instruction on top of 7 cycles per KB, so tiles whose boxes are small (the 256 x 128
+  // pair tile: 16 KB + 8 KB per K block) load 1.5x as many bytes per clock that way.
+  static constexpr int kKSub = kKSub_;
+  static constexpr int kBlockK = 64 * kKSub;
   static constexpr int kStages = kStages_;
   static constexpr int kEpiWarps = kEpiWarps_;     // 4 or 8
   static constexpr bool kIsBf16 = kIsBf16_;
@@ -176,6 +182,7 @@ struct GemmConfig {
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kBarrierBytes;
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static_assert(kKSub == 1 || (kKSub == 2 && kARows == kBlockM), "K blocks per stage");
   static_assert(kHalves == 1 || kHalves == 2, "halves");
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps");
   static_assert(kMmaN % 64 == 0 && kMmaN >= 64 && kMmaN <= 256, "MMA N");
@@ -505,7 +512,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   const int k_blocks = p.k_blocks;
   const int sk_factor = (kSplitK && Cfg::kHalves == 1) ? p.sk_factor : 0;   // even split: single-width tiles only
 
-  if constexpr (!kSplitK && !kBIsKN && !kAIsKM) {
+  if constexpr (!kSplitK && !kBIsKN && !kAIsKM && Cfg::kKSub == 1) {
     if (warp == 0 && p.early_prefetch > 0 && cluster_id < num_tiles) {
       // L2 prefetch of the first tile's first kStages K blocks (the boxes the producer loads first)
       if (elect_one()) {
@@ -593,7 +600,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           const int x = kb_phys * Cfg::kBlockK;
           if (issuer) {
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, tx_bytes);
-            if constexpr (!kAIsKM) {
+            if constexpr (Cfg::kKSub == 2) {
+              // one box per operand tile: both K blocks of the stage (uniform tiles only)
+              tma_load_3d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, 0, row_a, kb_phys * 2, pol);
+            } else if constexpr (!kAIsKM) {
               tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
             } else {
               // A[K, M]: coordinates are (row of C, K); two 64 x 64 boxes cover the CTA's 128 rows
@@ -604,7 +614,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             }
 #pragma unroll
             for (int h = 0; h < Cfg::kHalves; ++h) {
-              if constexpr (!kBIsKN) {
+              if constexpr (Cfg::kKSub == 2) {
+                tma_load_3d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, 0,
+                               row_b[h], kb_phys * 2, pol);
+              } else if constexpr (!kBIsKN) {
                 // one box of b_box rows at a time (a single box for uniform tiles)
 #pragma unroll 1
                 for (int j = 0; j < rows_b[h]; j += b_box)
@@ -719,8 +732,14 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               if (!skip_mma) {
                 umma_f16<G>(tmem_d, da, db, idesc_h[h], first_kb ? 0u : 1u);   // first K step of a segment overwrites
 #pragma unroll
-                for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k)
-                  umma_f16<G>(tmem_d, da + kAStepK * k, db + kBStepK * k, idesc_h[h], 1u);
+                for (int k = 1; k < Cfg::kBlockK / Cfg::kUmmaK; ++k) {
+                  // four steps inside a 64-element K block, then on to the stage's next K block (its own
+                  // K-major tile, right behind the first)
+                  constexpr uint32_t kASub = (uint32_t)(Cfg::kABytes / Cfg::kKSub) >> 4;
+                  constexpr uint32_t kBSub = (uint32_t)(Cfg::kBHalfBytes / Cfg::kKSub) >> 4;
+                  umma_f16<G>(tmem_d, da + kASub * (k >> 2) + kAStepK * (k & 3), db + kBSub * (k >> 2) + kBStepK * (k & 3),
+                              idesc_h[h], 1u);
+                }
               }
               if (last_kb) {                                             // this half's accumulator is complete
                 if (skip_mma) {

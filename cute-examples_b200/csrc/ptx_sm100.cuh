@@ -258,6 +258,24 @@ __device__ __forceinline__ uint64_t policy_evict_normal() {
 
 // ---------------------------------------------------------------- tcgen05 ---
 // TMEM allocation: one full warp; the base address is written to `smem_dst`.
+// The same for a 3-D tensor map (x: element inside a 128-byte row, y: row, z: 64-element K block).
+template <int kCtaGroup>
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
+                                            int32_t x, int32_t y, int32_t z, uint64_t policy) {
+  if constexpr (kCtaGroup == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+  }
+}
 template <int kCtaGroup>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   if constexpr (kCtaGroup == 1)

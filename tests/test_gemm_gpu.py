@@ -20,7 +20,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 DT = {0: torch.bfloat16, 1: torch.float16}
-NUM_CONFIGS = 11
+NUM_CONFIGS = 12
 
 
 @pytest.fixture(scope="module")
