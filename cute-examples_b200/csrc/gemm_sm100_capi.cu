@@ -365,7 +365,7 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // it moves 24 KB per K block and SM where the 128 x 128 tile moves 32 (8 % faster there).  The
 // 256 x 192 tile (8) is load-bound (0.80x) and is kept for tests: balanced tilings of the two
 // 256-column configurations cover its use.  Configuration 11 is 7 with two K blocks per TMA box:
-// 17-25 % faster on the few-tile shapes (1024 x 1024 x 4096: 15.6 against 20.7 us), K % 64 == 0 only.
+// 17-25 % faster on the few-tile shapes, K % 64 == 0 only (its rate is refined in make_plan).
 constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77};
 constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
@@ -377,9 +377,9 @@ constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0
 constexpr double kFanoutKBlocksPerOutput = 6.5;
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
-constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2; }
+constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2 || config == 11; }
 // Configurations whose K-split kernel also has the even split (single-width tiles).
-constexpr bool has_even_split(int config) { return config == 0 || config == 2; }
+constexpr bool has_even_split(int config) { return config == 0 || config == 2 || config == 11; }
 // Largest even split: a tile has 16 blocks of 32 rows x 64 columns to share out among its contributors.
 constexpr int kMaxEvenSplit = 16;
 // Configurations with a store-to-every-output kernel (the pair tiles of the multi-GPU path).
@@ -390,16 +390,16 @@ constexpr bool has_balanced(int config) { return config == 0 || config == 1 || c
 // Configurations with kernels for the other operand layouts and alpha / beta.
 constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // Even split: what cutting costs per wave of units on top of the K blocks, in K blocks of the
-// configuration's tile: about 12 us measured on B200 (counters zeroed by a memset node, partial
-// tiles written, the wait for the other contributors, one tile's worth of partial data read back
-// and stored; little of it overlaps the next unit's main loop).
-constexpr double kEvenSplitFixupKBlocks[kNumConfigs] = {43.0, 0.0, 32.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
-// K block time of a single wave of few, independently streaming CTAs relative to the full grid's.
-constexpr double kFewTileKBlockFactor[kNumConfigs] = {1.95, 1.0, 2.15, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0};
+// configuration's tile, as  fixed + per_range / ranges : measured on B200 about 6 us + 25 us / ranges
+// for the 256-column tiles (partial tiles written, the wait for the other contributors, a share of the
+// tile read back from every contributor and stored: the more contributors, the smaller the share) and
+// 6.5 us for the 128-column tile, whose partial tiles are half as large.
+constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0};
+constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // The exchange's cost for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile
 // in one cluster, partial sums exchanged through distributed shared memory: no workspace, no
-// counters, no trip through L2).
-constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {20.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+// counters, no trip through L2): 8 - 8.5 us for the 256-column tiles, 5.6 us for the 128-column one.
+constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0};
 
 // Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
 // one GPC, and a GPC of this generation has about 18 SMs.
@@ -508,7 +508,13 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     const long slots = cap / c.cta_group;
     const long waves = ceil_div(tiles, slots);
     if (!forced_config && kConfigRate[i] <= 0.0) continue;
-    const double rate = kConfigRate[i] > 0.0 ? kConfigRate[i] : 1.0;
+    double rate = kConfigRate[i] > 0.0 ? kConfigRate[i] : 1.0;
+    // The 256 x 128 tile with two K blocks per box: 1.2x configuration 7 when every SM is pulling
+    // operands (64 tiles), 1.33x with 32 tiles or fewer (1024 x 1024 x 4096: 15.6 against 20.7 us).
+    if (c.k_sub == 2 && tiles <= 32) rate = 0.88;
+    // A pair tile spends its second CTA on rows that do not exist when M <= 128 (and streams B in
+    // boxes of 64 rows): 128 x 8192 x 8192 took 43 us that way, 34.5 us with the 128-row tile cut along K.
+    if (c.cta_group == 2 && c.mma_n == 128 && M <= 128) rate *= 0.6;
     Plan cand;
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
@@ -608,20 +614,12 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     double even_cost = 1e300;
     if (allow_split && has_even_split(i) && g_opt_split_k != 0 && g_opt_split_k != 1) {
       const long sk_cluster = g_opt_sk_cluster.load();
-      // Which cut is best is decided with the K loop at the pace it has when few CTAs (pairs) each
-      // stream their own operands (measured: about twice the K block time of a full grid, while the
-      // cost of the exchange stays what it is); whether to cut at all, below, with the same units as
-      // the whole-tile cost.  With full-grid K block times four contributors in a cluster were
-      // preferred to eight through the workspace, which measured 4 us faster on
-      // 512..2048 x 128..2048 x 8192.
-      const double few = kFewTileKBlockFactor[i];
       double best_score = 1e300;
       auto consider = [&](int f, bool cluster, long waves_f, double fixup) {
-        const double per_wave = static_cast<double>(k_blocks) / f + boundary + fixup;
-        const double score = static_cast<double>(waves_f) * (per_wave + (few - 1.0) * k_blocks / f);
-        if (score < best_score) {
-          best_score = score;
-          even_cost = static_cast<double>(waves_f) * per_wave * block_n / rate;
+        const double c_f = static_cast<double>(waves_f) * (static_cast<double>(k_blocks) / f + boundary + fixup) * block_n / rate;
+        if (c_f < best_score) {
+          best_score = c_f;
+          even_cost = c_f;
           even_s = f;
           even_cluster = cluster;
         }
@@ -629,11 +627,14 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
       for (int f = 2; f <= kMaxEvenSplit; ++f) {
         if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
         if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
-        if (sk_cluster != 1 || (f != 2 && f != 4)) consider(f, false, ceil_div(tiles * f, slots), kEvenSplitFixupKBlocks[i]);
+        if (f > 4 * (c.mma_n / 64)) continue;               // a contributor's share is at least one 32 x 64 block
+        const bool cluster_ok = (f == 2 || f == 4) && c.mma_n / 64 % f == 0;   // and, in a cluster, whole 64-column chunks
+        if (sk_cluster != 1 || !cluster_ok)
+          consider(f, false, ceil_div(tiles * f, slots), kEvenSplitFixedKBlocks[i] + kEvenSplitPerRangeKBlocks[i] / f);
         // 2 or 4 contributors per tile: clusters of up to 8 CTAs, and every chunk that leaves a CTA has
         // a staging slot of its own in shared memory; one unit per CTA (pair), as many waves of
         // clusters as that takes
-        if (sk_cluster != 0 && (f == 2 || f == 4) && tiles * f * c.cta_group <= 65535)
+        if (sk_cluster != 0 && cluster_ok && tiles * f * c.cta_group <= 65535)
           consider(f, true, ceil_div(tiles, resident_clusters(sm_count, f * c.cta_group)), kClusterSplitFixupKBlocks[i]);
       }
     }

@@ -459,8 +459,48 @@ def test_random_shapes_library_plan_exact(capi, M, N, K, index):
     assert torch.equal(C.view(torch.int16), want.view(torch.int16)), plan_text(capi, M, N, K)
 
 
+@pytest.mark.parametrize("factor", [2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_even_split_of_the_narrow_pair_tile(capi, dtype, factor):
+    """The 256 x 128 pair tile with two K blocks per TMA box (configuration 11), cut into up to eight
+    K ranges through the workspace (its tile has eight 32 x 64 blocks to share out): inside the
+    tolerance on random operands, exact on integer-valued ones, ragged M and N."""
+    M, N, K = 300, 392, 128 * 4 * factor + 64
+    capi.gemm_sm100_set_option(b"tile_config", 11)
+    capi.gemm_sm100_set_option(b"split_k", factor)
+    capi.gemm_sm100_set_option(b"sk_cluster", 0)
+    text = plan_text(capi, M, N, K)
+    assert "config=11" in text and f"cut into {factor} K ranges" in text, text
+    A, B = oracle.make_inputs(M, N, K, 270 + factor, dtype)
+    C = run_capi(capi, A, B)
+    assert_close(C, oracle.c_gemm_tn_f32(A, B), dtype)
+    assert torch.equal(C.view(torch.int16), run_capi(capi, A, B).view(torch.int16))
+    At, Bt = oracle.make_ternary_inputs(M, N, 256, 271, dtype)
+    At = torch.cat([At, torch.zeros(M, K - 256, dtype=dtype)], dim=1)
+    Bt = torch.cat([Bt, torch.zeros(N, K - 256, dtype=dtype)], dim=1)
+    perm = torch.randperm(K, generator=torch.Generator().manual_seed(272))
+    At, Bt = At[:, perm].contiguous(), Bt[:, perm].contiguous()
+    Ct = run_capi(capi, At, Bt)
+    assert torch.equal(Ct.view(torch.int16), oracle.c_gemm_tn(At, Bt).view(torch.int16))
+
+
+def test_two_k_blocks_per_box_needs_whole_k_blocks(capi):
+    """Configuration 11 describes the operands as 64-element K blocks, so K must be a multiple of 64:
+    forced on any other K it is ignored and the library's own choice runs; odd numbers of K blocks
+    (the second half of the last box lies outside the tensor and reads as zeros) are fine."""
+    capi.gemm_sm100_set_option(b"tile_config", 11)
+    assert "config=11" not in plan_text(capi, 512, 512, 1000)
+    for K in (64, 192, 1088):
+        assert "config=11" in plan_text(capi, 512, 512, K)
+        A, B = oracle.make_ternary_inputs(300, 264, K, 273)
+        A[:, 256:] = 0
+        B[:, 256:] = 0
+        C = run_capi(capi, A, B)
+        assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16)), K
+
+
 # configuration, ranges per tile: the contributors of a tile form one cluster (pair tile: two CTAs per contributor)
-CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4)]
+CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2)]
 
 
 @pytest.mark.parametrize("config,factor", CLUSTER_SPLITS)
