@@ -115,7 +115,9 @@ KSPLIT_VARIANTS = ("c0:tile_config=0,split_k=0;c3:tile_config=3,split_k=0;c2s:ti
                    "c2e2:tile_config=2,split_k=2,sk_cluster=0;c2e4:tile_config=2,split_k=4,sk_cluster=0;"
                    "c2e8:tile_config=2,split_k=8;c2e16:tile_config=2,split_k=16;"
                    "c0k2:tile_config=0,split_k=2,sk_cluster=1;c0k4:tile_config=0,split_k=4,sk_cluster=1;"
-                   "c2k2:tile_config=2,split_k=2,sk_cluster=1;c2k4:tile_config=2,split_k=4,sk_cluster=1;auto;mm")
+                   "c2k2:tile_config=2,split_k=2,sk_cluster=1;c2k4:tile_config=2,split_k=4,sk_cluster=1;"
+                   "c11:tile_config=11,split_k=0;c11k2:tile_config=11,split_k=2,sk_cluster=1;"
+                   "c11e4:tile_config=11,split_k=4;c11e8:tile_config=11,split_k=8;auto;mm")
 
 
 def parse_variants(text):
@@ -209,6 +211,7 @@ def ab_table(shapes, variants, dtype, rounds, iters, scratch, fanout=None, coold
                "flush": scratch is not None, "cooldown_s": cooldown,
                "auto": gk.describe_config(gk.select_config(M, N, K, gk.DTYPE_CODES[dtype])),
                "auto_workspace_bytes": gk.workspace_bytes(M, N, K, gk.DTYPE_CODES[dtype]),
+               "auto_plan": gk.describe_plan(M, N, K, gk.DTYPE_CODES[dtype]),
                "us": {k: round(statistics.median(v), 2) for k, v in res.items()},
                "min_us": {k: round(min(v), 2) for k, v in res.items()},
                "ratio_to_first": {k: round(statistics.median(v) / statistics.median(res[first]), 4)
