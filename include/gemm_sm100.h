@@ -183,13 +183,17 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
 /* Tuning / test knobs, process-wide.  Set them before asking gemm_sm100_workspace_bytes, which
  * depends on them.
  *   "tile_config"  -1 = choose automatically (default), otherwise an index reported by
- *                  gemm_sm100_describe_config.
+ *                  gemm_sm100_describe_config.  A configuration that cannot take the problem
+ *                  (more rows than its A tile holds; K not a multiple of 64 for the one that
+ *                  loads two K blocks per TMA box) is ignored and the automatic choice runs.
  *   "timeout_ms"   bound of each device-side wait, 1..60000, default 2000.
  *   "max_ctas"     0 = all SMs (default); otherwise caps the persistent grid.
  *   "split_k"      -1 = automatic (default); 0 = never; 1 = contiguous K ranges, one per CTA or
  *                  pair, whenever the chosen configuration has a K-split variant; 2..16 = every
  *                  tile cut into that many equal K ranges with the reduction spread over the
- *                  contributors (256 x 256 and 128 x 256 tiles).
+ *                  contributors (256 x 256 and 128 x 256 tiles; 2..8 for the 256 x 128 tile with
+ *                  two K blocks per TMA box).  A forced value the chosen configuration cannot
+ *                  take is ignored.
  *   "sk_cluster"   how the contributors of a tile cut into 2 or 4 K ranges exchange their partial
  *                  sums: 1 = always inside a thread-block cluster (one cluster per tile, one range
  *                  per CTA or pair, partial tiles moved between the CTAs' shared memories by
