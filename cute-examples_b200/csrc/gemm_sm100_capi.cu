@@ -38,7 +38,7 @@ constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 12;
+constexpr int kNumConfigs = 13;
 
 struct ConfigInfo {
   int cta_group, mma_n, halves, stages, epi_warps;
@@ -68,6 +68,9 @@ constexpr ConfigInfo kConfigs[kNumConfigs] = {
     // 256 x 128 pair tile with two K blocks per stage (K % 64 == 0 only): half as many, twice as
     // large TMA boxes as configuration 7
     {2, 128, 1, 4, 4, 128, 0, 2},
+    // 128 x 128 single-CTA tile with two K blocks per stage, for problems of at most 128 rows whose
+    // columns give too few 256-wide tiles: twice the tiles of configuration 2, half-size partial tiles
+    {1, 128, 1, 3, 4, 128, 0, 2},
 };
 
 template <int kIndex, bool kIsBf16>
@@ -366,8 +369,8 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // 256 x 192 tile (8) is load-bound (0.80x) and is kept for tests: balanced tilings of the two
 // 256-column configurations cover its use.  Configuration 11 is 7 with two K blocks per TMA box:
 // 17-25 % faster on the few-tile shapes, K % 64 == 0 only (its rate is refined in make_plan).
-constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77};
-constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77, 0.71};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
 // in K blocks of that tile.  Trace counters with all outputs in local memory (32768 x 4096 x 8192):
 // the MMA issuer's wait for a free accumulator grows from 2.6 % of the loop with one output to 6.4 %
@@ -377,9 +380,9 @@ constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0
 constexpr double kFanoutKBlocksPerOutput = 6.5;
 constexpr int kSplitKConfig = 2;                      // K-split configuration of the static-scratch entry point
 // Configurations that have a K-split variant: the 256 x 512 pair tile and the 128 x 256 tile.
-constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2 || config == 11; }
+constexpr bool has_split_k(int config) { return config == 0 || config == 1 || config == 2 || config == 11 || config == 12; }
 // Configurations whose K-split kernel also has the even split (single-width tiles).
-constexpr bool has_even_split(int config) { return config == 0 || config == 2 || config == 11; }
+constexpr bool has_even_split(int config) { return config == 0 || config == 2 || config == 11 || config == 12; }
 // Largest even split: a tile has 16 blocks of 32 rows x 64 columns to share out among its contributors.
 constexpr int kMaxEvenSplit = 16;
 // Configurations with a store-to-every-output kernel (the pair tiles of the multi-GPU path).
@@ -394,12 +397,12 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // for the 256-column tiles (partial tiles written, the wait for the other contributors, a share of the
 // tile read back from every contributor and stored: the more contributors, the smaller the share) and
 // 6.5 us for the 128-column tile, whose partial tiles are half as large.
-constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0};
-constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0, 35.0};
+constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // The exchange's cost for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile
 // in one cluster, partial sums exchanged through distributed shared memory: no workspace, no
 // counters, no trip through L2): 8 - 8.5 us for the 256-column tiles, 5.6 us for the 128-column one.
-constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0};
+constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0, 30.0};
 
 // Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
 // one GPC, and a GPC of this generation has about 18 SMs.
@@ -515,6 +518,10 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     // A pair tile spends its second CTA on rows that do not exist when M <= 128 (and streams B in
     // boxes of 64 rows): 128 x 8192 x 8192 took 43 us that way, 34.5 us with the 128-row tile cut along K.
     if (c.cta_group == 2 && c.mma_n == 128 && M <= 128) rate *= 0.6;
+    // The 128 x 128 tile with two K blocks per box pays for problems of 65-128 rows (128 x 4096 x 8192: 19.7 us
+    // cut in four against 22.3 us for the 128 x 256 tile cut in nine); with fewer rows the wider tile's
+    // smaller partial tiles win (64 x 4096 x 8192: 20.8 against 19.8 us).
+    if (c.cta_group == 1 && c.k_sub == 2 && M <= 64) rate *= 0.85;
     Plan cand;
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
@@ -1009,6 +1016,7 @@ int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cuda
     case 9: return launch_config<9, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 10: return launch_config<10, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 11: return launch_config<11, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 12: return launch_config<12, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }

@@ -20,7 +20,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 DT = {0: torch.bfloat16, 1: torch.float16}
-NUM_CONFIGS = 12
+NUM_CONFIGS = 13
 
 
 @pytest.fixture(scope="module")
@@ -461,16 +461,18 @@ def test_random_shapes_library_plan_exact(capi, M, N, K, index):
 
 @pytest.mark.parametrize("factor", [2, 3, 4, 8])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_even_split_of_the_narrow_pair_tile(capi, dtype, factor):
-    """The 256 x 128 pair tile with two K blocks per TMA box (configuration 11), cut into up to eight
-    K ranges through the workspace (its tile has eight 32 x 64 blocks to share out): inside the
-    tolerance on random operands, exact on integer-valued ones, ragged M and N."""
+@pytest.mark.parametrize("config", [11, 12])
+def test_even_split_of_the_narrow_tiles(capi, config, dtype, factor):
+    """The 128-column tiles with two K blocks per TMA box (256 x 128 pair tile: configuration 11,
+    128 x 128 single-CTA tile: 12), cut into up to eight K ranges through the workspace (such a tile
+    has eight 32 x 64 blocks to share out): inside the tolerance on random operands, exact on
+    integer-valued ones, ragged M and N."""
     M, N, K = 300, 392, 128 * 4 * factor + 64
-    capi.gemm_sm100_set_option(b"tile_config", 11)
+    capi.gemm_sm100_set_option(b"tile_config", config)
     capi.gemm_sm100_set_option(b"split_k", factor)
     capi.gemm_sm100_set_option(b"sk_cluster", 0)
     text = plan_text(capi, M, N, K)
-    assert "config=11" in text and f"cut into {factor} K ranges" in text, text
+    assert f"config={config}" in text and f"cut into {factor} K ranges" in text, text
     A, B = oracle.make_inputs(M, N, K, 270 + factor, dtype)
     C = run_capi(capi, A, B)
     assert_close(C, oracle.c_gemm_tn_f32(A, B), dtype)
@@ -500,7 +502,7 @@ def test_two_k_blocks_per_box_needs_whole_k_blocks(capi):
 
 
 # configuration, ranges per tile: the contributors of a tile form one cluster (pair tile: two CTAs per contributor)
-CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2)]
+CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2), (12, 2)]
 
 
 @pytest.mark.parametrize("config,factor", CLUSTER_SPLITS)
