@@ -42,6 +42,7 @@ def run(M, N, K, config, flags, warm=3):
     C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     gk.set_option("tile_config", config)
     gk.set_option("balance", 0)              # uniform tiles: the ideal cycle count below assumes them
+    gk.set_option("split_k", 0)              # whole tiles: the K-split kernels through the workspace keep no trace
     gk.set_option("debug_flags", flags)
     trace = torch.zeros(gk.num_sms() * WORDS, dtype=torch.int64, device="cuda")
     if FANOUT > 0:
@@ -64,6 +65,7 @@ def run(M, N, K, config, flags, warm=3):
         gk.set_option("debug_flags", 0)
         gk.set_option("tile_config", -1)
         gk.set_option("balance", 1)
+        gk.set_option("split_k", -1)
     gk.device_status()
     return trace.cpu().numpy().reshape(-1, WORDS).astype(np.float64), start.elapsed_time(end)
 
