@@ -452,30 +452,29 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
   ctx.status = p.status;
   ctx.timeout_ns = p.timeout_ns;
 
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_b);
-    for (int d = 0; d < num_c; ++d) prefetch_tensormap(tmap_c + d);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_base + kFullOff + 8u * s, 1);    // leader's producer arrives once and posts the byte count
-      mbar_init(bar_base + kEmptyOff + 8u * s, 1);   // one tcgen05.commit per use
+  if (threadIdx.x < 32) {
+    if (threadIdx.x == 0) {
+      *abort_flag = 0;
+      prefetch_tensormap(&tmap_a);
+      prefetch_tensormap(&tmap_b);
+      for (int d = 0; d < num_c; ++d) prefetch_tensormap(tmap_c + d);
+      if constexpr (kSplitK) {
+        // every epilogue warp of every contributor to this CTA's rows arrives once on each
+        const uint32_t arrivals = (uint32_t)(Cfg::kEpiWarps * (p.sk_cluster > 0 ? p.sk_factor : 1));
+        mbar_init(bar_base + kRxReadyOff, arrivals);
+        // the other contributors' copies into this CTA's receive area are counted in bytes
+        mbar_init(bar_base + kRxDoneOff, 1);
+      }
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(bar_base + kTFullOff + 8u * a, 1);                     // one tcgen05.commit per use
-      mbar_init(bar_base + kTEmptyOff + 8u * a, Cfg::kEpiWarps * G);   // every epilogue warp of the pair arrives once
-    }
-    mbar_init(bar_base + kTmemReadyOff, 1);   // pair mode: the peer's TMEM allocation is done
-    if constexpr (kSplitK) {
-      // every epilogue warp of every contributor to this CTA's rows arrives once on each
-      const uint32_t arrivals = (uint32_t)(Cfg::kEpiWarps * (p.sk_cluster > 0 ? p.sk_factor : 1));
-      mbar_init(bar_base + kRxReadyOff, arrivals);
-      // the other contributors' copies into this CTA's receive area are counted in bytes
-      mbar_init(bar_base + kRxDoneOff, 1);
-    }
+    // One barrier per lane (they sit 8 bytes apart in the order full[], empty[], tfull[2], tempty[2],
+    // tmem_ready).  full: the leader's producer arrives once and posts the byte count; empty and
+    // tfull: one tcgen05.commit per use; tempty: every epilogue warp of the pair arrives once;
+    // tmem_ready (pair mode): the peer's TMEM allocation is done.
+    for (uint32_t b = threadIdx.x; b < 2u * kStages + 5u; b += 32u)
+      mbar_init(bar_base + 8u * b, (b == 2u * kStages + 2u || b == 2u * kStages + 3u) ? Cfg::kEpiWarps * G : 1);
     fence_mbar_init();
     if constexpr (kSplitK) {
-      if (p.sk_cluster > 0)
+      if (threadIdx.x == 0 && p.sk_cluster > 0)
         mbar_arrive_expect_tx(bar_base + kRxDoneOff,
                               (uint32_t)(Cfg::kBlockM * Cfg::kBlockN * 4 / p.sk_factor * (p.sk_factor - 1)));
     }
