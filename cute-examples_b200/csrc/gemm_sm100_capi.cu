@@ -613,7 +613,7 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
         split_cost *= 1.15;                                  // the fit is good to about 10 %: ties go to whole tiles
       }
     }
-    const bool can_split = allow_split && has_split_k(i) && units >= 2;
+    const bool can_split = allow_split && has_split_k(i) && units >= 2 && c.k_sub == 1;   // contiguous ranges: 64-element K blocks only
     // Even split: every tile cut into s equal K ranges, the reduction spread over the contributors.
     // Forced with split_k = s (2..16); automatic when it beats whole tiles and the contiguous ranges.
     int even_s = 0;
