@@ -514,7 +514,7 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     double rate = kConfigRate[i] > 0.0 ? kConfigRate[i] : 1.0;
     // The 256 x 128 tile with two K blocks per box: 1.2x configuration 7 when every SM is pulling
     // operands (64 tiles), 1.33x with 32 tiles or fewer (1024 x 1024 x 4096: 15.6 against 20.7 us).
-    if (c.k_sub == 2 && tiles <= 32) rate = 0.88;
+    if (c.k_sub == 2 && c.cta_group == 2 && tiles <= 32) rate = 0.88;
     // A pair tile spends its second CTA on rows that do not exist when M <= 128 (and streams B in
     // boxes of 64 rows): 128 x 8192 x 8192 took 43 us that way, 34.5 us with the 128-row tile cut along K.
     if (c.cta_group == 2 && c.mma_n == 128 && M <= 128) rate *= 0.6;
