@@ -641,8 +641,12 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
         // 2 or 4 contributors per tile: clusters of up to 8 CTAs, and every chunk that leaves a CTA has
         // a staging slot of its own in shared memory; one unit per CTA (pair), as many waves of
         // clusters as that takes
-        if (sk_cluster != 0 && cluster_ok && tiles * f * c.cta_group <= 65535)
-          consider(f, true, ceil_div(tiles, resident_clusters(sm_count, f * c.cta_group)), kClusterSplitFixupKBlocks[i]);
+        if (sk_cluster != 0 && cluster_ok && tiles * f * c.cta_group <= 65535) {
+          // only the 32-row groups that exist are exchanged: with few rows the exchange is mostly its
+          // fixed part (16 x 8192 x 8192 cut in four: 29.4 us, 33.6 us when all 128 rows were sent)
+          const double live = M >= 128 ? 1.0 : 0.4 + 0.15 * static_cast<double>(ceil_div(M, 32));
+          consider(f, true, ceil_div(tiles, resident_clusters(sm_count, f * c.cta_group)), kClusterSplitFixupKBlocks[i] * live);
+        }
       }
     }
     const double best_other = (can_split && auto_split) ? split_cost : cost;

@@ -474,9 +474,16 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       mbar_init(bar_base + 8u * b, (b == 2u * kStages + 2u || b == 2u * kStages + 3u) ? Cfg::kEpiWarps * G : 1);
     fence_mbar_init();
     if constexpr (kSplitK) {
-      if (threadIdx.x == 0 && p.sk_cluster > 0)
+      if (threadIdx.x == 0 && p.sk_cluster > 0) {
+        // What the other contributors will send: for every epilogue warp whose 32 rows exist (rows
+        // past M are not exchanged), the chunks of this CTA's share, 8 KB each.
+        int m_tile, n_tile;
+        tile_coords((int)(blockIdx.x / G) / p.sk_factor, p, m_tile, n_tile);
+        const int rows = p.M - (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
+        const int live_warps = rows <= 0 ? 0 : (rows >= Cfg::kBlockM ? 4 : (rows + 31) / 32);
         mbar_arrive_expect_tx(bar_base + kRxDoneOff,
-                              (uint32_t)(Cfg::kBlockM * Cfg::kBlockN * 4 / p.sk_factor * (p.sk_factor - 1)));
+                              (uint32_t)(live_warps * (p.sk_factor - 1) * (Cfg::kBlockN / 64 / p.sk_factor) * 8192));
+      }
     }
   }
   // Barriers are initialised: let the producer go.  The TMEM allocation (slow for a CTA pair)
@@ -881,6 +888,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               // for one chunk is 8 KB in one piece: written to a staging slot of its own (every
               // chunk that leaves the CTA has one, nothing is reused) and moved by one asynchronous
               // copy that is counted on the owner's barrier.  The own share goes straight into place.
+              if (row0 >= p.M) return;                          // none of this warp's rows exist: nothing to exchange
               const int owner = piece0 >> rx_share_shift;
               const int local0 = piece0 - (owner << rx_share_shift);
               const uint32_t rx_off = (uint32_t)((((seg.part * 4 + q) << rx_share_shift) + local0) * 512);

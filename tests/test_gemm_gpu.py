@@ -506,7 +506,10 @@ CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2), (12, 2)]
 
 
 @pytest.mark.parametrize("config,factor", CLUSTER_SPLITS)
-@pytest.mark.parametrize("shape", [(256, 512, 4096), (300, 520, 2048 + 64), (100, 264, 1024), (1024, 2048, 1024)])
+@pytest.mark.parametrize("shape", [(256, 512, 4096), (300, 520, 2048 + 64), (100, 264, 1024), (1024, 2048, 1024),
+                                   # few rows: only the epilogue warps whose rows exist exchange anything (one, two
+                                   # of four; the second CTA of a pair none, or one)
+                                   (16, 520, 2048), (40, 264, 4096), (128, 264, 2048), (130, 520, 2048)])
 def test_cluster_split_matches_oracle_and_global_split(capi, config, factor, shape):
     """Even K-split whose partial sums travel through distributed shared memory: no workspace, one
     unit per CTA (pair), as many waves of clusters as the tiles need (the last shape: 256 to 512
