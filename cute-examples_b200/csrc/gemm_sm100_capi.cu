@@ -38,7 +38,7 @@ constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 13;
+constexpr int kNumConfigs = 15;
 
 struct ConfigInfo {
   int cta_group, mma_n, halves, stages, epi_warps;
@@ -71,6 +71,10 @@ constexpr ConfigInfo kConfigs[kNumConfigs] = {
     // 128 x 128 single-CTA tile with two K blocks per stage, for problems of at most 128 rows whose
     // columns give too few 256-wide tiles: twice the tiles of configuration 2, half-size partial tiles
     {1, 128, 1, 3, 4, 128, 0, 2},
+    // 128 x 64 tiles for problems of at most 16 / 64 rows and several thousand columns: four K blocks
+    // (512 bytes of every row) per TMA box, short A
+    {1, 64, 1, 5, 4, 16, 1, 4},
+    {1, 64, 1, 3, 4, 64, 1, 4},
 };
 
 template <int kIndex, bool kIsBf16>
@@ -208,16 +212,16 @@ inline long tma_store_cols(long n) { return n >= 8 ? (n & ~7L) : 8; }
 
 // Tensor map of a row-major 2-D array of 16-bit elements: `rows` x `cols`, pitch `ld`
 // elements, box `box_rows` x 64 columns, 128-byte swizzle (64 x 2 B = one swizzle row).
-// With k_sub == 2 (cols a multiple of 64) the same array is described as 3-D: 64 elements x rows x
-// 64-element K blocks (128 bytes apart), box 64 x box_rows x 2, so that one copy brings two K blocks
-// of the rows, each as its own K-major tile.
+// With k_sub > 1 (cols a multiple of 64) the same array is described as 3-D: 64 elements x rows x
+// 64-element K blocks (128 bytes apart), box 64 x box_rows x k_sub, so that one copy brings k_sub K
+// blocks of the rows, each as its own K-major tile.
 int encode_2d(CUtensorMap* map, const void* base, int dtype, long rows, long cols, long ld,
               int box_rows, int* cuda_error_out, int k_sub = 1) {
-  const bool blocks = k_sub == 2;
+  const bool blocks = k_sub > 1;
   const cuuint64_t dims[3] = {blocks ? 64u : static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
                               static_cast<cuuint64_t>(cols / 64)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2u, 128u};
-  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 2u};
+  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(k_sub)};
   const cuuint32_t elem_strides[3] = {1u, 1u, 1u};
   const CUtensorMapDataType dt =
       dtype == GEMM_SM100_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -369,8 +373,8 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // 256 x 192 tile (8) is load-bound (0.80x) and is kept for tests: balanced tilings of the two
 // 256-column configurations cover its use.  Configuration 11 is 7 with two K blocks per TMA box:
 // 17-25 % faster on the few-tile shapes, K % 64 == 0 only (its rate is refined in make_plan).
-constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77, 0.71};
-constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77, 0.71, 0.62, 0.55};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
 // in K blocks of that tile.  Trace counters with all outputs in local memory (32768 x 4096 x 8192):
 // the MMA issuer's wait for a free accumulator grows from 2.6 % of the loop with one output to 6.4 %
@@ -397,12 +401,12 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // for the 256-column tiles (partial tiles written, the wait for the other contributors, a share of the
 // tile read back from every contributor and stored: the more contributors, the smaller the share) and
 // 6.5 us for the 128-column tile, whose partial tiles are half as large.
-constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0, 35.0};
-constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0, 35.0, 0.0, 0.0};
+constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // The exchange's cost for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile
 // in one cluster, partial sums exchanged through distributed shared memory: no workspace, no
 // counters, no trip through L2): 8 - 8.5 us for the 256-column tiles, 5.6 us for the 128-column one.
-constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0, 30.0};
+constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0, 30.0, 0.0, 0.0};
 
 // Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
 // one GPC, and a GPC of this generation has about 18 SMs.
@@ -504,9 +508,13 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
   for (int i = first; i < last; ++i) {
     const ConfigInfo& c = kConfigs[i];
     if (c.a_rows < 128 && M > c.a_rows) continue;        // few-row configurations: only what their A tile holds
-    if (c.k_sub == 2 && K % 64 != 0) continue;           // whole 64-element K blocks only (nothing bounds K inside a block)
+    if (c.k_sub > 1 && K % 64 != 0) continue;           // whole 64-element K blocks only (nothing bounds K inside a block)
     const int block_n = c.mma_n * c.halves;
     const long tiles = ceil_div(M, 128L * c.cta_group) * ceil_div(N, block_n);
+    // The 64-column few-row tiles stream B well only when most SMs have one (16 x 8192 x 8192: 27.5 us
+    // against 29.8 for the wider tile cut along K; 64 x 6144 x 4096: 14.2 against 18.6; but 16 x 4096 x 8192,
+    // 64 tiles: 24.0 against 18.2).
+    if (c.k_sub == 4 && !forced_config && tiles < 96) continue;
     const int cap = grid_cap(c, sm_count);
     const long slots = cap / c.cta_group;
     const long waves = ceil_div(tiles, slots);
@@ -1021,6 +1029,8 @@ int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cuda
     case 10: return launch_config<10, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 11: return launch_config<11, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 12: return launch_config<12, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 13: return launch_config<13, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 14: return launch_config<14, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }

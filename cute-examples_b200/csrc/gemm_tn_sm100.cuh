@@ -182,7 +182,7 @@ struct GemmConfig {
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kBarrierBytes;
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
-  static_assert(kKSub == 1 || (kKSub == 2 && kARows == kBlockM), "K blocks per stage");
+  static_assert(kKSub == 1 || kKSub == 2 || kKSub == 4, "K blocks per stage");
   static_assert(kHalves == 1 || kHalves == 2, "halves");
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps");
   static_assert(kMmaN % 64 == 0 && kMmaN >= 64 && kMmaN <= 256, "MMA N");
@@ -606,9 +606,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
           const int x = kb_phys * Cfg::kBlockK;
           if (issuer) {
             if (is_leader) mbar_arrive_expect_tx(bar_base + kFullOff + 8u * s, tx_bytes);
-            if constexpr (Cfg::kKSub == 2) {
-              // one box per operand tile: both K blocks of the stage (uniform tiles only)
-              tma_load_3d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, 0, row_a, kb_phys * 2, pol);
+            if constexpr (Cfg::kKSub > 1) {
+              // one box per operand tile: all K blocks of the stage (uniform tiles only)
+              tma_load_3d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, 0, row_a, kb_phys * Cfg::kKSub, pol);
             } else if constexpr (!kAIsKM) {
               tma_load_2d<G>(smem_a + s * Cfg::kABytes, &tmap_a, full_leader + 8u * s, x, row_a, pol);
             } else {
@@ -620,9 +620,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
             }
 #pragma unroll
             for (int h = 0; h < Cfg::kHalves; ++h) {
-              if constexpr (Cfg::kKSub == 2) {
+              if constexpr (Cfg::kKSub > 1) {
                 tma_load_3d<G>(smem_b + s * Cfg::kBBytes + h * Cfg::kBHalfBytes, &tmap_b, full_leader + 8u * s, 0,
-                               row_b[h], kb_phys * 2, pol);
+                               row_b[h], kb_phys * Cfg::kKSub, pol);
               } else if constexpr (!kBIsKN) {
                 // one box of b_box rows at a time (a single box for uniform tiles)
 #pragma unroll 1
