@@ -616,10 +616,13 @@ def run_multi(args):
     # short blocks after an idle gap, run in the boost state and make the exchange look expensive.
     for _ in range(3 * max(args.steps, 10)):
         local_step()
+    # Three rounds, each starting at another variant: a block inherits the temperature its
+    # predecessor left, and a fixed order would pin the hottest slot on one of the three.
     ours_ms, mm_ms, fused_ms = [], [], []
-    for _ in range(2):
-        for fn, acc in ((step, fused_ms), (local_step, ours_ms), (mm_step, mm_ms)):
-            acc.append(time_steps(fn, args.steps, torch.cuda.synchronize, barrier) / 2)
+    order = [(step, fused_ms), (local_step, ours_ms), (mm_step, mm_ms)]
+    for r in range(3):
+        for fn, acc in order[r:] + order[:r]:
+            acc.append(time_steps(fn, args.steps, torch.cuda.synchronize, barrier) / 3)
     gk.device_status()
     local_total, mm_total = sum(ours_ms), sum(mm_ms)
     t = torch.tensor([local_total, mm_total, sum(fused_ms)], dtype=torch.float64, device=device)
@@ -668,7 +671,7 @@ def run_multi(args):
                         "local_gemm_ms_per_step": round(local_ms, 4),
                         "local_gemm_note": "max over ranks of the rank's own slab GEMM without any exchange: blocks of "
                                            "`steps` back-to-back launches, in turn with blocks of the whole step and "
-                                           "of cuBLAS (torch.mm) on the same slab, two blocks each, after a run-in",
+                                           "of cuBLAS (torch.mm) on the same slab, three blocks each with a rotating order, after a run-in",
                         "local_gemm_ms_per_rank": local_ms_per_rank,
                         "cublas_slab_ms_per_step": round(cublas_ms, 4),
                         "cublas_slab_ms_per_rank": cublas_ms_per_rank,
