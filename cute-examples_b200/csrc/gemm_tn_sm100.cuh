@@ -527,7 +527,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
         const TileCols tc = tile_columns<Cfg>(n_tile, p);
         const int row_a = (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
         const int rot = p.k_rotate == 1 ? (int)(((long long)cluster_id * k_blocks) / num_tiles) : 0;
-        const int stages = k_blocks < kStages ? k_blocks : kStages;
+        // two stages' worth: every prefetch is a TMA instruction of its own (about 130 cycles each), and
+        // they sit in front of the first loads when there is no previous kernel to hide them under
+        const int stages = k_blocks < 2 ? k_blocks : 2;
         for (int kb = 0; kb < stages; ++kb) {
           int kb_phys = kb + rot;
           if (kb_phys >= k_blocks) kb_phys -= k_blocks;
