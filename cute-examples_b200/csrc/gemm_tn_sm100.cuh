@@ -77,7 +77,7 @@ struct TileParams {
   int bal_q, bal_rem, bal_start;
   int b_box_rows;  // rows per TMA box of B: kBRows for uniform tiles, 64 / kCtaGroup for balanced ones
   // > 0: before waiting for the previous kernel of the stream (programmatic dependent launch), the
-  // producer asks L2 for the operand boxes of its first ring of stages.  A prefetch is only a hint
+  // producer asks L2 for the operand boxes of its first two stages.  A prefetch is only a hint
   // and L2 is where this GPU's writes become visible, so it is safe whatever that kernel still
   // writes; it puts the DRAM reads of this launch's first stages under that kernel's tail.
   int early_prefetch;

@@ -206,7 +206,7 @@ int gemm_sm100_device_status(unsigned int* status_out, int* cuda_error_out);
  *                  CTAs are scheduled while it drains, set up their barriers and tensor memory,
  *                  and wait for its completion before they touch global memory; after any other
  *                  kernel the launch is an ordinary one.  0 = ordinary launches only.
- *   "early_prefetch" 1 = with "pdl", every CTA asks L2 for the operand boxes of its first ring of
+ *   "early_prefetch" 1 = with "pdl", every CTA asks L2 for the operand boxes of its first two
  *                  stages before it waits for the previous kernel (default; a hint only: L2 is
  *                  where this GPU's writes become visible, so nothing stale can be read later);
  *                  0 = off.
