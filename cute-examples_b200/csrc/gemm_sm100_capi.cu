@@ -528,8 +528,8 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     if (c.cta_group == 2 && c.mma_n == 128 && M <= 128) rate *= 0.6;
     // The 128 x 128 tile with two K blocks per box pays for problems of 65-128 rows (128 x 4096 x 8192: 19.7 us
     // cut in four against 22.3 us for the 128 x 256 tile cut in nine); with fewer rows the wider tile's
-    // smaller partial tiles win (64 x 4096 x 8192: 20.8 against 19.8 us).
-    if (c.cta_group == 1 && c.k_sub == 2 && M <= 64) rate *= 0.85;
+    // smaller partial tiles win (64 x 4096 x 8192: 20.5 against 19.8 us, 16 x 4096 x 8192: 20.7 against 18.2).
+    if (c.cta_group == 1 && c.k_sub == 2 && M <= 64) rate *= 0.65;
     Plan cand;
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
@@ -643,7 +643,10 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
         if (g_opt_split_k > 1 && f != g_opt_split_k) continue;
         if (f > slots || k_blocks < 8L * f || tiles * f > 0x3fffffff / 64) continue;
         if (f > 4 * (c.mma_n / 64)) continue;               // a contributor's share is at least one 32 x 64 block
-        const bool cluster_ok = (f == 2 || f == 4) && c.mma_n / 64 % f == 0;   // and, in a cluster, whole 64-column chunks
+        // in a cluster a share is made of whole 64-column chunks, or (twice as many contributors as
+        // chunks) of one chunk of one half of the rows
+        const int chunks = c.mma_n / 64;
+        const bool cluster_ok = (f == 2 || f == 4) && (chunks % f == 0 || f == 2 * chunks);
         if (sk_cluster != 1 || !cluster_ok)
           consider(f, false, ceil_div(tiles * f, slots), kEvenSplitFixedKBlocks[i] + kEvenSplitPerRangeKBlocks[i] / f);
         // 2 or 4 contributors per tile: clusters of up to 8 CTAs, and every chunk that leaves a CTA has

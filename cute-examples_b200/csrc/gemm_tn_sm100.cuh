@@ -477,12 +477,20 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
       if (threadIdx.x == 0 && p.sk_cluster > 0) {
         // What the other contributors will send: for every epilogue warp whose 32 rows exist (rows
         // past M are not exchanged), the chunks of this CTA's share, 8 KB each.
+        // More contributors than 64-column chunks (four for a 128-column tile): a share is one chunk
+        // of one half of the rows, so only the warps of that half send to this CTA.
+        constexpr int kTileChunks = Cfg::kBlockN / 64;
+        const int unit = (int)(blockIdx.x / G);
         int m_tile, n_tile;
-        tile_coords((int)(blockIdx.x / G) / p.sk_factor, p, m_tile, n_tile);
+        tile_coords(unit / p.sk_factor, p, m_tile, n_tile);
         const int rows = p.M - (m_tile * G + (int)cta_rank) * Cfg::kBlockM;
-        const int live_warps = rows <= 0 ? 0 : (rows >= Cfg::kBlockM ? 4 : (rows + 31) / 32);
-        mbar_arrive_expect_tx(bar_base + kRxDoneOff,
-                              (uint32_t)(live_warps * (p.sk_factor - 1) * (Cfg::kBlockN / 64 / p.sk_factor) * 8192));
+        const int row_groups = p.sk_factor > kTileChunks ? p.sk_factor / kTileChunks : 1;
+        const int warps = 4 / row_groups;                       // epilogue warps (32 rows each) per share
+        const int first_row = ((unit % p.sk_factor) % row_groups) * warps * 32;
+        const int mine = rows - first_row;                      // rows of this CTA's share that exist
+        const int live_warps = mine <= 0 ? 0 : (mine >= warps * 32 ? warps : (mine + 31) / 32);
+        const int chunks = row_groups > 1 ? 1 : kTileChunks / p.sk_factor;
+        mbar_arrive_expect_tx(bar_base + kRxDoneOff, (uint32_t)(live_warps * (p.sk_factor - 1) * chunks * 8192));
       }
     }
   }
@@ -810,14 +818,21 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
     // cluster K-split: a contributor's share of the tile's 16-byte pieces (kBlockN / 4 of them) is
     // 2^rx_share_shift pieces wide
     int rx_share_shift = 0;
+    int rx_row_groups = 1;
     int remote_chunks = 0;                                   // chunks this warp has sent to other CTAs so far
     constexpr uint32_t kRxBytes = Cfg::kBlockM * Cfg::kBlockN * 4;   // receive area: one fp32 partial tile, at the start of the ring
     if constexpr (kSplitK && Cfg::kHalves == 1) {
       static_assert(Cfg::kEpiWarps != 4 || kStages * Cfg::kStageBytes + Cfg::kEpiBytes >= (int)kRxBytes + 4 * 3 * 8192,
                     "ring + epilogue staging must hold the receive area and three staging slots per warp");
-      if (cluster_split)
+      if (cluster_split) {
         while (((Cfg::kBlockN / 4) >> rx_share_shift) > sk_factor) ++rx_share_shift;
+        if (sk_factor > Cfg::kBlockN / 64) {                   // a share is one chunk of one group of row quarters
+          rx_row_groups = sk_factor / (Cfg::kBlockN / 64);
+          rx_share_shift = 4;
+        }
+      }
     }
+    const int rx_warps = 4 / rx_row_groups;                  // row quarters (epilogue warps) per share
     for (; ok && work.next(seg); ++iter) {
       int m_tile, n_tile;
       tile_coords(seg.tile, p, m_tile, n_tile);
@@ -891,9 +906,12 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               // chunk that leaves the CTA has one, nothing is reused) and moved by one asynchronous
               // copy that is counted on the owner's barrier.  The own share goes straight into place.
               if (row0 >= p.M) return;                          // none of this warp's rows exist: nothing to exchange
-              const int owner = piece0 >> rx_share_shift;
-              const int local0 = piece0 - (owner << rx_share_shift);
-              const uint32_t rx_off = (uint32_t)((((seg.part * 4 + q) << rx_share_shift) + local0) * 512);
+              // owner of this warp's chunk: by columns, and (more contributors than chunks) by row group
+              const int by_cols = piece0 >> rx_share_shift;
+              const int owner = by_cols * rx_row_groups + q / rx_warps;
+              const int local0 = piece0 - (by_cols << rx_share_shift);
+              const uint32_t rx_off =
+                  (uint32_t)((((seg.part * rx_warps + q % rx_warps) << rx_share_shift) + local0) * 512);
               uint32_t dst = smem_a + rx_off;
               if (owner != seg.part) dst = smem_a + kRxBytes + (uint32_t)(q * 3 + remote_chunks) * 8192u;
 #pragma unroll
@@ -1088,12 +1106,13 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tmap_a, const CU
               if (trace && warp == 2 && lane == 0) trace[kTraceRxDone] = clock64();
             const int share = 1 << rx_share_shift;                // pieces (of 4 columns) in this CTA's share
             const int row = (m_tile * G + (int)cta_rank) * Cfg::kBlockM + my_row;
-            const int col_first = n_tile * Cfg::kBlockN + seg.part * share * 4;
-            if (row < p.M && !(kDebug && (dbg & kDebugSkipStores))) {
+            const int col_first = n_tile * Cfg::kBlockN + (seg.part / rx_row_groups) * share * 4;
+            const bool my_rows = q / rx_warps == seg.part % rx_row_groups;   // this warp's rows are in the share
+            if (row < p.M && my_rows && !(kDebug && (dbg & kDebugSkipStores))) {
               uint16_t* crow = reinterpret_cast<uint16_t*>(p.c_ptr) + (long long)row * p.ldc + col_first;
-              // [sender][row quarter][piece][row]: this thread's row of piece l from sender i
-              const float4* rx = reinterpret_cast<const float4*>(smem) + ((size_t)(q * share) * 32 + lane);
-              const size_t sender_stride = (size_t)4 * share * 32;
+              // [sender][row quarter of the share][piece][row]: this thread's row of piece l from sender i
+              const float4* rx = reinterpret_cast<const float4*>(smem) + ((size_t)((q % rx_warps) * share) * 32 + lane);
+              const size_t sender_stride = (size_t)rx_warps * share * 32;
 #pragma unroll 1
               for (int l = 0; l < share; l += 2) {                 // two pieces = 8 columns = 16 bytes of C
                 const int col = col_first + l * 4;

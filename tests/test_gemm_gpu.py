@@ -502,7 +502,7 @@ def test_two_k_blocks_per_box_needs_whole_k_blocks(capi):
 
 
 # configuration, ranges per tile: the contributors of a tile form one cluster (pair tile: two CTAs per contributor)
-CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2), (12, 2)]
+CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2), (12, 2), (11, 4), (12, 4)]
 
 
 @pytest.mark.parametrize("config,factor", CLUSTER_SPLITS)
