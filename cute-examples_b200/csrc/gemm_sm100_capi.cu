@@ -38,7 +38,7 @@ constexpr size_t kStaticScratchBytes = kStaticFlagBytes + 5u * 1024u * 1024u;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-constexpr int kNumConfigs = 15;
+constexpr int kNumConfigs = 16;
 
 struct ConfigInfo {
   int cta_group, mma_n, halves, stages, epi_warps;
@@ -75,6 +75,8 @@ constexpr ConfigInfo kConfigs[kNumConfigs] = {
     // (512 bytes of every row) per TMA box, short A
     {1, 64, 1, 5, 4, 16, 1, 4},
     {1, 64, 1, 3, 4, 64, 1, 4},
+    // configuration 9 with two K blocks per box (K % 64 == 0): 16 x 28672 x 8192 74.5 against 75.6 us
+    {1, 256, 1, 3, 4, 16, 1, 2},
 };
 
 template <int kIndex, bool kIsBf16>
@@ -373,8 +375,8 @@ inline long ceil_div(long a, long b) { return (a + b - 1) / b; }
 // 256 x 192 tile (8) is load-bound (0.80x) and is kept for tests: balanced tilings of the two
 // 256-column configurations cover its use.  Configuration 11 is 7 with two K blocks per TMA box:
 // 17-25 % faster on the few-tile shapes, K % 64 == 0 only (its rate is refined in make_plan).
-constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77, 0.71, 0.62, 0.55};
-constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kConfigRate[kNumConfigs] = {0.95, 1.0, 0.72, 0.5, 0.0, 0.0, 0.0, 0.63, 0.70, 0.80, 0.76, 0.77, 0.71, 0.62, 0.55, 0.815};
+constexpr double kTileBoundaryKBlocks[kNumConfigs] = {0.0, 2.5, 0.0, 0.0, 2.5, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // Store-to-every-output kernel, 256 x 512 tile: exposed epilogue time per output beyond the first,
 // in K blocks of that tile.  Trace counters with all outputs in local memory (32768 x 4096 x 8192):
 // the MMA issuer's wait for a free accumulator grows from 2.6 % of the loop with one output to 6.4 %
@@ -401,12 +403,12 @@ constexpr bool has_layouts(int config) { return config >= 0 && config <= 3; }
 // for the 256-column tiles (partial tiles written, the wait for the other contributors, a share of the
 // tile read back from every contributor and stored: the more contributors, the smaller the share) and
 // 6.5 us for the 128-column tile, whose partial tiles are half as large.
-constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0, 35.0, 0.0, 0.0};
-constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+constexpr double kEvenSplitFixedKBlocks[kNumConfigs] = {21.0, 0.0, 16.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 44.0, 35.0, 0.0, 0.0, 0.0};
+constexpr double kEvenSplitPerRangeKBlocks[kNumConfigs] = {89.0, 0.0, 68.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 // The exchange's cost for the cluster K-split (2 or 4 ranges per tile, the contributors of a tile
 // in one cluster, partial sums exchanged through distributed shared memory: no workspace, no
 // counters, no trip through L2): 8 - 8.5 us for the 256-column tiles, 5.6 us for the 128-column one.
-constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0, 30.0, 0.0, 0.0};
+constexpr double kClusterSplitFixupKBlocks[kNumConfigs] = {29.0, 0.0, 23.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 38.0, 30.0, 0.0, 0.0, 0.0};
 
 // Clusters of `cluster_ctas` CTAs (one CTA per SM) the device holds at once: a cluster sits inside
 // one GPC, and a GPC of this generation has about 18 SMs.
@@ -529,7 +531,7 @@ Plan make_plan(int M, int N, int K, int sm_count, bool allow_split = true, int c
     // The 128 x 128 tile with two K blocks per box pays for problems of 65-128 rows (128 x 4096 x 8192: 19.7 us
     // cut in four against 22.3 us for the 128 x 256 tile cut in nine); with fewer rows the wider tile's
     // smaller partial tiles win (64 x 4096 x 8192: 20.5 against 19.8 us, 16 x 4096 x 8192: 20.7 against 18.2).
-    if (c.cta_group == 1 && c.k_sub == 2 && M <= 64) rate *= 0.65;
+    if (c.cta_group == 1 && c.k_sub == 2 && c.mma_n == 128 && M <= 64) rate *= 0.65;
     Plan cand;
     cand.config = i;
     cand.ctas = static_cast<int>((tiles < slots ? tiles : slots) * c.cta_group);
@@ -1034,6 +1036,7 @@ int dispatch(const Plan& plan, const Problem& p, void* ws, DeviceState& st, cuda
     case 12: return launch_config<12, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 13: return launch_config<13, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     case 14: return launch_config<14, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
+    case 15: return launch_config<15, kIsBf16>(p, plan, ws, st, stream, cuda_error_out);
     default: return GEMM_SM100_ERR_BAD_OPTION;
   }
 }

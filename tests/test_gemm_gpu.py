@@ -20,7 +20,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 DT = {0: torch.bfloat16, 1: torch.float16}
-NUM_CONFIGS = 15
+NUM_CONFIGS = 16
 
 
 @pytest.fixture(scope="module")
@@ -879,14 +879,14 @@ def test_tile_256x192_covers_ragged_columns(capi):
 
 
 @pytest.mark.parametrize("config,M", [(9, 1), (9, 8), (9, 16), (10, 17), (10, 40), (10, 64),
-                                      (13, 1), (13, 9), (13, 16), (14, 17), (14, 33), (14, 64)])
+                                      (13, 1), (13, 9), (13, 16), (14, 17), (14, 33), (14, 64), (15, 1), (15, 16)])
 @pytest.mark.parametrize("N,K", [(1000, 2056), (3584, 512), (264, 64)])
 def test_short_a_tile_configurations(capi, config, M, N, K):
     """The few-row configurations load only 16 / 64 rows of A per stage; the MMA's other operand rows
     are whatever follows in the ring and land in accumulator rows nobody reads.  C sits inside a
     sentinel-filled buffer: rows below and above it must stay untouched, the live rows exact
     (ternary operands) and inside the tolerance (seeded operands)."""
-    if config in (13, 14) and K % 64:
+    if config in (13, 14, 15) and K % 64:
         K = K // 64 * 64 + 64          # several K blocks per TMA box: whole 64-element K blocks only
     capi.gemm_sm100_set_option(b"tile_config", config)
     assert f"config={config} " in plan_text(capi, M, N, K)
@@ -917,7 +917,8 @@ def test_short_a_tile_configurations_refuse_taller_problems(capi):
     A, B = oracle.make_inputs(100, 520, 264, 222)
     assert_close(run_capi(capi, A, B), oracle.c_gemm_tn_f32(A, B), torch.bfloat16)
     capi.gemm_sm100_set_option(b"tile_config", -1)
-    assert "config=9 " in plan_text(capi, 16, 28672, 8192)
+    assert "config=15 " in plan_text(capi, 16, 28672, 8192)     # K a multiple of 64: two K blocks per box
+    assert "config=9 " in plan_text(capi, 16, 28672, 8192 + 8)
     assert "config=10 " in plan_text(capi, 64, 28672, 8192)
     assert "config=2 " in plan_text(capi, 128, 28672, 8192)
 
@@ -949,7 +950,7 @@ def test_balanced_column_tiling_fp16_exact(capi, config, N, tiles_n):
     assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16))
 
 
-@pytest.mark.parametrize("config,M", [(9, 16), (10, 48), (13, 16), (14, 48)])
+@pytest.mark.parametrize("config,M", [(9, 16), (10, 48), (13, 16), (14, 48), (15, 16)])
 def test_short_a_tile_configurations_fp16(capi, config, M):
     N, K = 2048 + 8, 1024 + 64
     capi.gemm_sm100_set_option(b"tile_config", config)
