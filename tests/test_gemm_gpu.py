@@ -501,6 +501,17 @@ def test_two_k_blocks_per_box_needs_whole_k_blocks(capi):
         assert torch.equal(C.view(torch.int16), oracle.c_gemm_tn(A, B).view(torch.int16)), K
 
 
+def test_resident_clusters_query(capi):
+    """How many clusters of 2 / 4 / 8 one-CTA-per-SM blocks the device holds (the planner's wave count
+    for the cluster K-split): positive, never more CTAs than SMs, fewer clusters the larger they are."""
+    sms = capi.gemm_sm100_num_sms()
+    held = [capi.gemm_sm100_resident_clusters(n) for n in (2, 4, 8)]
+    assert all(h > 0 for h in held), held
+    assert all(h * n <= sms for h, n in zip(held, (2, 4, 8))), (held, sms)
+    assert held[0] >= held[1] >= held[2]
+    assert capi.gemm_sm100_resident_clusters(3) < 0
+
+
 # configuration, ranges per tile: the contributors of a tile form one cluster (pair tile: two CTAs per contributor)
 CLUSTER_SPLITS = [(0, 2), (0, 4), (2, 2), (2, 4), (11, 2), (12, 2), (11, 4), (12, 4)]
 
